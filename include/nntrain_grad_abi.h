@@ -1,0 +1,228 @@
+/*
+ * C ABI of libnntrain_grad_b200.so: the compressed data-parallel gradient
+ * path (BFP8 block codec, BFP8 / BF16 gradient reducers, fused clip-norm) as
+ * hand-written sm_100a CUDA kernels.
+ *
+ * Conventions (those of the reference's native layer, NNtrain.Cuda/native):
+ *   - every entry point returns an int cudaError_t (0 = success; bad
+ *     arguments = cudaErrorInvalidValue = 1);
+ *   - kernel launches are asynchronous; the return value is the launch status;
+ *   - pointers are raw device addresses unless stated otherwise; streams and
+ *     events are the CUDA runtime's handles passed as opaque pointers;
+ *   - the caller owns every buffer; the library owns only what one of its
+ *     create calls returned and frees it only in the paired destroy call;
+ *   - NaN / Inf in the data is not a status: it raises a device-side flag the
+ *     caller reads once per step.
+ *
+ * Each declaration cites the reference interface it replaces (path within the
+ * reference project : lines).  Entry points marked "ABI minor 36" have no
+ * counterpart in the reference, whose compressed reducers take exactly two
+ * devices of one process; they carry the same path to N ranks.
+ */
+#ifndef NNTRAIN_GRAD_ABI_H
+#define NNTRAIN_GRAD_ABI_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* nntrain_stream_t;   /* cudaStream_t */
+typedef void* nntrain_event_t;    /* cudaEvent_t  */
+
+/* NNtrain.Cuda/native/cuda_runtime_bridge.cu:74-82 */
+typedef struct nntrain_native_error_info {
+    uint32_t struct_size;
+    uint32_t abi_version;
+    uint64_t sequence;
+    int32_t status;
+    int32_t device;
+    uint32_t operation;
+    uint32_t reserved;
+} nntrain_native_error_info;
+
+/* ---- process-level ------------------------------------------------------ */
+
+/* (major << 16) | minor; major 1, minor 36.
+ * cuda_runtime_bridge.cu:18-21,1436-1438 */
+uint32_t nntrain_abi_version(void);
+/* cuda_runtime_bridge.cu:1440-1450 */
+int nntrain_last_error(nntrain_native_error_info* destination, size_t destination_size);
+/* cuda_runtime_bridge.cu:1452-1481 */
+int nntrain_error_snapshot(int status, int device, uint32_t operation,
+                           nntrain_native_error_info* destination, size_t destination_size);
+/* Bits 1 (bfloat16), 6 (asynchronous gradient reduction), 7 (CUDA graphs),
+ * 8 (BFP8 quantization) on compute capability >= 10.
+ * cuda_runtime_bridge.cu:1483-1536 */
+int nntrain_capability_bitmap(int device, unsigned long long* bitmap,
+                              int* compute_capability_major, int* compute_capability_minor);
+/* Thread-local device selection cache.  cuda_runtime_bridge.cu:122-131,2336-2339 */
+int nntrain_cuda_set_device(int device);
+/* Thread-local stream used by the entry points that take none.
+ * NNtrain.Cuda/native/tensor_kernels.cu:26,2888-2891 */
+int nntrain_cuda_use_external_stream(void* stream);
+
+/* ---- BFP8 block codec ---------------------------------------------------
+ * payload: signed int8 per value; scales: one fp32 per block,
+ * scale = max|x| == 0 ? 1 : max|x| / 127; code = clamp(rne(x / scale), +-127).
+ * quantization_block_size >= length selects one tensor-wide scale. */
+
+/* cuda_runtime_bridge.cu:1540-1622 */
+int nntrain_cuda_bfp8_quantize_f32(int device, const float* source, signed char* payload,
+                                   float* scales, int length, int quantization_block_size,
+                                   void* stream);
+/* cuda_runtime_bridge.cu:1720-1768 */
+int nntrain_cuda_bfp8_dequantize_f32(int device, const signed char* payload, const float* scales,
+                                     float* destination, int length, int quantization_block_size,
+                                     void* stream);
+/* Encode and overwrite the source with its decode; rejects the tensor-wide
+ * case.  cuda_runtime_bridge.cu:1770-1826 */
+int nntrain_cuda_bfp8_quantize_f32_roundtrip(int device, float* source, signed char* payload,
+                                             float* scales, int length, int quantization_block_size,
+                                             void* stream);
+/* ABI minor 36.  64-bit length; block_size 0 = tensor-wide.  Optional
+ * outputs, each enabled by a non-null pointer: roundtrip (decode, may alias
+ * source), squared_sum (+= sum of squares of the decoded values, binary64),
+ * finite_status (= 1 when any input is NaN/Inf). */
+int nntrain_bfp8_block_encode(int device, const float* source, signed char* payload, float* scales,
+                              long long length, int block_size, float* roundtrip,
+                              double* squared_sum, int* finite_status, void* stream);
+/* ABI minor 36. */
+int nntrain_bfp8_block_decode(int device, const signed char* payload, const float* scales,
+                              float* destination, long long length, int block_size, void* stream);
+
+/* ---- tensor-wide BFP8 gradient publication and 2-device reducer ----------- */
+
+/* Finite check, tensor-wide scale, payload, fp32 gradient overwritten with
+ * its decode.  NaN/Inf: *finite_status = 1, scale = 1, nothing else written.
+ * tensor_kernels.cu:988-1042,1114-1146,3876-3889 */
+int nntrain_bfp8_gradient_quantize(int device, float* source, signed char* payload, float* scale,
+                                   int length, int* finite_status, nntrain_stream_t stream);
+/* Same plus *squared_sum += sum of squares of the decoded values.
+ * tensor_kernels.cu:1044-1073,3891-3905 */
+int nntrain_bfp8_gradient_quantize_accumulate(int device, float* source, signed char* payload,
+                                              float* scale, int length, int* finite_status,
+                                              double* squared_sum, nntrain_stream_t stream);
+/* tensor_kernels.cu:1044-1073,3907-3921 */
+int nntrain_bfp8_gradient_squared_sum(int device, const signed char* payload, const float* scale,
+                                      int length, double* squared_sum, int* finite_status,
+                                      nntrain_stream_t stream);
+/* Scale-only clip: scale = fmaxf(scale * multiplier, FLT_MIN).
+ * tensor_kernels.cu:1075-1082,3923-3933 */
+int nntrain_bfp8_gradient_scale(int device, float* scale, float multiplier, nntrain_stream_t stream);
+/* tensor_kernels.cu:3935-4002 */
+int nntrain_bfp8_gradient_reduce(
+    int primary_device, int secondary_device, const signed char* local_payload,
+    const float* local_scale, const signed char* remote_payload, const float* remote_scale,
+    signed char* remote_payload_staging, float* remote_scale_staging, float* reduced,
+    signed char* output_payload, float* output_scale, int length, float reduction_scale,
+    int* finite_status, const int* remote_finite_status, int* remote_status_staging,
+    double* squared_sum, nntrain_stream_t communication_stream, nntrain_event_t local_ready,
+    nntrain_event_t remote_ready, nntrain_event_t reduced_ready);
+/* tensor_kernels.cu:4004-4038 */
+int nntrain_bfp8_gradient_broadcast(
+    int destination_device, int source_device, const signed char* source_payload,
+    const float* source_scale, signed char* destination_payload, float* destination_scale,
+    float* destination_float, int length, int* destination_finite_status,
+    nntrain_stream_t destination_stream, nntrain_event_t source_ready);
+
+/* ---- bucketed BF16 / block-128 BFP8 transport (two devices, one process) --- */
+
+/* NNtrain.Cuda/native/gradient_collectives.cu:213-219 */
+int nntrain_gradient_comm_create(int device, nntrain_stream_t* stream);
+/* gradient_collectives.cu:221-227 */
+int nntrain_gradient_event_create(int device, nntrain_event_t* event);
+/* gradient_collectives.cu:11-22,229-239 */
+int nntrain_gradient_pack_bf16(int device, const float* source, void* destination_bf16,
+                               int destination_offset, int length, nntrain_stream_t compute_stream);
+/* gradient_collectives.cu:24-60,241-252 */
+int nntrain_gradient_pack_bfp8_block(int device, const float* source, signed char* destination,
+                                     float* scales, int length, nntrain_stream_t compute_stream);
+/* gradient_collectives.cu:254-258 */
+int nntrain_gradient_record_ready(int device, nntrain_event_t event, nntrain_stream_t compute_stream);
+/* gradient_collectives.cu:260-270 */
+int nntrain_gradient_record_ready_external(int device, nntrain_event_t event,
+                                           nntrain_stream_t compute_stream);
+/* gradient_collectives.cu:62-90,272-309 */
+int nntrain_gradient_exchange_bf16(int destination_device, int source_device, const void* local_bf16,
+                                   const void* remote_source_bf16, void* remote_staging_bf16,
+                                   float* reduced, int length, double* squared_sum,
+                                   nntrain_stream_t communication_stream, nntrain_event_t local_ready,
+                                   nntrain_event_t remote_ready);
+/* gradient_collectives.cu:92-129,311-357 */
+int nntrain_gradient_exchange_bfp8_block(
+    int destination_device, int source_device, const signed char* local, const float* local_scales,
+    const signed char* remote_source, const float* remote_source_scales, signed char* remote_staging,
+    float* remote_staging_scales, float* reduced, int length, double* squared_sum,
+    nntrain_stream_t communication_stream, nntrain_event_t local_ready, nntrain_event_t remote_ready);
+/* gradient_collectives.cu:359-414 */
+int nntrain_gradient_host_pipeline_create(int source_device, int destination_device,
+                                          int chunk_elements, void** pipeline_pointer);
+/* gradient_collectives.cu:416-474 */
+int nntrain_gradient_host_pipeline_create_bfp8_block(int source_device, int destination_device,
+                                                     int chunk_elements, void** pipeline_pointer);
+/* gradient_collectives.cu:476-578 */
+int nntrain_gradient_host_pipeline_exchange_bf16(void* pipeline_pointer, const void* local_bf16,
+                                                 const void* remote_source_bf16, float* reduced,
+                                                 int length, double* squared_sum,
+                                                 nntrain_event_t local_ready,
+                                                 nntrain_event_t remote_ready);
+/* gradient_collectives.cu:580-703 */
+int nntrain_gradient_host_pipeline_exchange_bfp8_block(
+    void* pipeline_pointer, const signed char* local, const float* local_scales,
+    const signed char* remote_source, const float* remote_source_scales, float* reduced, int length,
+    double* squared_sum, nntrain_event_t local_ready, nntrain_event_t remote_ready);
+/* gradient_collectives.cu:705-709 */
+int nntrain_gradient_host_pipeline_destroy(void* pipeline_pointer);
+/* gradient_collectives.cu:131-141,711-721 */
+int nntrain_gradient_unpack_float(int device, const float* source, int source_offset,
+                                  float* destination, int length,
+                                  nntrain_stream_t communication_stream);
+/* gradient_collectives.cu:723-727 */
+int nntrain_gradient_comm_synchronize(int device, nntrain_stream_t communication_stream);
+/* gradient_collectives.cu:729-733 */
+int nntrain_gradient_event_destroy(int device, nntrain_event_t event);
+/* gradient_collectives.cu:735-739 */
+int nntrain_gradient_comm_destroy(int device, nntrain_stream_t communication_stream);
+
+/* ---- norm / clip ---------------------------------------------------------- */
+
+/* These four run on the thread's implicit stream.
+ * tensor_kernels.cu:968-986,3229-3231 */
+int nntrain_tensor_squared_sum(const float* values, int length, double* result);
+/* tensor_kernels.cu:910-914,3177-3180 */
+int nntrain_tensor_scale(float* values, int length, float scale);
+/* tensor_kernels.cu:931-936,3208-3211 */
+int nntrain_tensor_encode_bf16(const float* source, unsigned short* destination, int length);
+/* tensor_kernels.cu:2876-2881,3870-3874 */
+int nntrain_tensor_decode_bf16(const unsigned short* source, float* destination, int length);
+/* NNtrain.Cuda/native/pure_bfloat16_gradients.cu:315-335,546-557 */
+int nntrain_tensor_bf16_gradient_squared_sum(const unsigned short* values, int length, double* result,
+                                             nntrain_stream_t stream);
+/* pure_bfloat16_gradients.cu:337-348,559-570 */
+int nntrain_tensor_bf16_gradient_scale(unsigned short* values, int length, float multiplier,
+                                       nntrain_stream_t stream);
+/* ABI minor 36.  kind 0 = fp32, 1 = bf16, 2 = BFP8 payload (+scales, block
+ * size; 0 = tensor-wide).  *squared_sum += sum of squares in binary64. */
+int nntrain_gradient_squared_sum(int device, int kind, const void* values, const float* scales,
+                                 long long length, int block_size, double* squared_sum,
+                                 int* finite_status, nntrain_stream_t stream);
+/* ABI minor 36.  Device-side clip coefficient (NNtrain.Core/Torch/nn.cs:69-72):
+ * out[0] = norm = (float)sqrt(*squared_sum); out[1] = norm > max_norm ?
+ * max_norm / (norm + 1e-6f) : 1. */
+int nntrain_gradient_clip_coefficient(int device, const double* squared_sum, float max_norm,
+                                      float* norm_and_coefficient, nntrain_stream_t stream);
+/* ABI minor 36.  Whole-arena clip.  kind 0: fp32 *= c (nn.cs:72-78); kind 1:
+ * bf16 = rn(f32 * c) (pure_bfloat16_gradients.cu:337-348); kind 2: values is
+ * the fp32 scale sidecar, scale = fmaxf(scale * c, FLT_MIN), payload untouched
+ * (tensor_kernels.cu:1075-1082).  With a non-null `coefficient` (kind 2) the
+ * multiplier is coefficient[1] read on the device. */
+int nntrain_gradient_clip_apply(int device, int kind, void* values, long long count, float multiplier,
+                                const float* coefficient, nntrain_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NNTRAIN_GRAD_ABI_H */

@@ -1,0 +1,122 @@
+// ABI gate, error ring, per-thread device / stream selection and the
+// capability bitmap: the few process-level exports the reference's managed
+// gateway probes before it uses the gradient path
+// (NNtrain.Cuda/native/cuda_runtime_bridge.cu:74-131,1436-1536,2336-2339;
+//  NNtrain.Cuda/native/tensor_kernels.cu:2888-2891).
+#include "common.cuh"
+
+#include <array>
+#include <mutex>
+
+namespace ngb {
+namespace {
+
+constexpr std::size_t kRingCapacity = 64;
+std::mutex g_error_mutex;
+std::uint64_t g_error_sequence = 0;
+std::array<ErrorInfo, kRingCapacity> g_error_ring{};
+ErrorInfo g_last_error{sizeof(ErrorInfo), kAbiVersion, 0, 0, -1, kOpNone, 0};
+
+thread_local int t_selected_device = -1;
+thread_local cudaStream_t t_implicit_stream = nullptr;
+
+constexpr int kMaxDevices = 64;
+int g_sm_counts[kMaxDevices] = {};
+
+}  // namespace
+
+int complete(Operation operation, int device, int status) {
+    if (status == static_cast<int>(cudaSuccess)) return status;
+    std::lock_guard<std::mutex> guard(g_error_mutex);
+    const std::uint64_t sequence = ++g_error_sequence;
+    ErrorInfo entry{sizeof(ErrorInfo), kAbiVersion, sequence, status, device,
+                    static_cast<std::uint32_t>(operation), 0};
+    g_last_error = entry;
+    g_error_ring[(sequence - 1) % kRingCapacity] = entry;
+    return status;
+}
+
+int select_device(int device) {
+    if (t_selected_device == device) return static_cast<int>(cudaSuccess);
+    cudaError_t status = cudaSetDevice(device);
+    if (status == cudaSuccess) t_selected_device = device;
+    return static_cast<int>(status);
+}
+
+cudaStream_t& implicit_stream() { return t_implicit_stream; }
+
+int sm_count() {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return 148;
+    int cached = g_sm_counts[device];
+    if (cached > 0) return cached;
+    int count = 0;
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
+        count = 148;
+    g_sm_counts[device] = count;
+    return count;
+}
+
+}  // namespace ngb
+
+using namespace ngb;
+
+NNTRAIN_EXPORT std::uint32_t nntrain_abi_version() { return kAbiVersion; }
+
+NNTRAIN_EXPORT int nntrain_last_error(ErrorInfo* destination, size_t destination_size) {
+    if (!destination || destination_size < sizeof(ErrorInfo))
+        return static_cast<int>(cudaErrorInvalidValue);
+    std::lock_guard<std::mutex> guard(g_error_mutex);
+    *destination = g_last_error;
+    return static_cast<int>(cudaSuccess);
+}
+
+// Finds the newest ring entry matching (status, device, operation).
+NNTRAIN_EXPORT int nntrain_error_snapshot(int status, int device, std::uint32_t operation,
+                                          ErrorInfo* destination, size_t destination_size) {
+    if (!destination || destination_size < sizeof(ErrorInfo))
+        return static_cast<int>(cudaErrorInvalidValue);
+    std::lock_guard<std::mutex> guard(g_error_mutex);
+    const std::uint64_t live = g_error_sequence < kRingCapacity ? g_error_sequence : kRingCapacity;
+    for (std::uint64_t back = 0; back < live; ++back) {
+        const std::uint64_t sequence = g_error_sequence - back;
+        const ErrorInfo& entry = g_error_ring[(sequence - 1) % kRingCapacity];
+        if (entry.sequence == sequence && entry.status == status && entry.device == device &&
+            entry.operation == operation) {
+            *destination = entry;
+            return static_cast<int>(cudaSuccess);
+        }
+    }
+    return static_cast<int>(cudaErrorInvalidValue);
+}
+
+// Bits as the reference defines them (cuda_runtime_bridge.cu:1505-1516); this
+// library implements only the gradient path, so it reports bit 1 (bfloat16),
+// bit 6 (asynchronous gradient reduction), bit 7 (CUDA graphs: every local
+// kernel here is capturable) and bit 8 (BFP8 quantization).
+NNTRAIN_EXPORT int nntrain_capability_bitmap(int device, unsigned long long* bitmap,
+                                             int* compute_capability_major,
+                                             int* compute_capability_minor) {
+    if (!bitmap || !compute_capability_major || !compute_capability_minor)
+        return complete(kOpCapabilities, device, static_cast<int>(cudaErrorInvalidValue));
+    int major = 0, minor = 0;
+    cudaError_t status = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+    if (status == cudaSuccess)
+        status = cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device);
+    if (status != cudaSuccess) return complete(kOpCapabilities, device, static_cast<int>(status));
+    unsigned long long features = 0;
+    if (major >= 10) features = (1ull << 1) | (1ull << 6) | (1ull << 7) | (1ull << 8);
+    *bitmap = features;
+    *compute_capability_major = major;
+    *compute_capability_minor = minor;
+    return static_cast<int>(cudaSuccess);
+}
+
+NNTRAIN_EXPORT int nntrain_cuda_set_device(int device) {
+    return complete(kOpSetDevice, device, select_device(device));
+}
+
+NNTRAIN_EXPORT int nntrain_cuda_use_external_stream(void* stream) {
+    implicit_stream() = reinterpret_cast<cudaStream_t>(stream);
+    return static_cast<int>(cudaSuccess);
+}

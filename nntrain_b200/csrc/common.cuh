@@ -1,0 +1,183 @@
+// Shared plumbing for the gradient-path library: export macro, status
+// recording, per-thread device selection, launch geometry, and the small
+// device helpers every kernel uses (IEEE scale / code arithmetic, vector
+// access, block-wide reductions).
+//
+// All translation units are compiled for sm_100a WITHOUT fast-math and with
+// -fmad=false: the codec must agree bit for bit with the reference's CPU codec
+// (NNtrain.Core/Tensors/Bfp8Quantization.cs:188-274), which neither flushes
+// subnormals nor fuses a multiply into an add.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cfloat>
+#include <cmath>
+#include <cstddef>
+#include <cstdint>
+
+#define NNTRAIN_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace ngb {
+
+// ---- ABI / status ---------------------------------------------------------
+// Same numbering as the reference's native layer
+// (NNtrain.Cuda/native/cuda_runtime_bridge.cu:18-21,23-72).
+constexpr std::uint32_t kAbiMajor = 1;
+constexpr std::uint32_t kAbiMinor = 36;   // 35 = reference; 36 adds the N-rank exports
+constexpr std::uint32_t kAbiVersion = (kAbiMajor << 16) | kAbiMinor;
+
+enum Operation : std::uint32_t {
+    kOpNone = 0,
+    kOpSetDevice = 3,
+    kOpCapabilities = 25,
+    kOpBfp8Quantize = 26,
+    kOpBfp8DequantizeF32 = 27,
+};
+
+struct ErrorInfo {            // layout of nntrain_native_error_info (:74-82)
+    std::uint32_t struct_size;
+    std::uint32_t abi_version;
+    std::uint64_t sequence;
+    std::int32_t status;
+    std::int32_t device;
+    std::uint32_t operation;
+    std::uint32_t reserved;
+};
+
+// Records a failed status in the error ring and returns it unchanged; the
+// success path takes no lock.
+int complete(Operation operation, int device, int status);
+
+// Thread-local device cache: cudaSetDevice only when the thread's selection
+// changes (cuda_runtime_bridge.cu:122-131).
+int select_device(int device);
+
+// Thread-local "current stream" used by the exports that take no stream
+// argument (NNtrain.Cuda/native/tensor_kernels.cu:26,2888-2891).
+cudaStream_t& implicit_stream();
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+// Persistent-style grid: enough CTAs to fill every SM `per_sm` times, never
+// more than the work needs.
+inline int grid_for(long long work_items, int per_sm) {
+    long long cap = static_cast<long long>(sm_count()) * per_sm;
+    if (work_items < 1) work_items = 1;
+    return static_cast<int>(work_items < cap ? work_items : cap);
+}
+
+constexpr int kThreads = 256;
+constexpr int kWarpsPerCta = kThreads / 32;
+constexpr int kCtasPerSm = 8;
+
+// ---- device helpers -------------------------------------------------------
+#ifdef __CUDACC__
+
+// scale = max == 0 ? 1 : max / 127, one IEEE division
+// (Bfp8Quantization.cs:217; cuda_runtime_bridge.cu:138-140).
+__device__ __forceinline__ float scale_from_maximum(float maximum) {
+    return maximum == 0.0f ? 1.0f : __fdiv_rn(maximum, 127.0f);
+}
+
+// Round-half-even of a quotient to an integer in [-127,127], NaN -> 0
+// (Bfp8Quantization.cs:220-227), kept in "biased" form: the returned float is
+// code + 1.5 * 2^23, whose low mantissa byte is the two's-complement int8
+// code.  Adding 1.5 * 2^23 performs the binary32 round-to-nearest-even to an
+// integer exactly for |q| <= 2^22; the quotient is clamped first, which
+// commutes with the rounding because the bounds are integers.  Everything
+// stays on the FP32/integer pipes (no F2I / I2F conversions).
+constexpr float kRoundMagic = 12582912.0f;
+
+__device__ __forceinline__ float biased_code(float quotient) {
+    float q = (quotient == quotient) ? quotient : 0.0f;
+    q = fminf(fmaxf(q, -127.0f), 127.0f);
+    return __fadd_rn(q, kRoundMagic);
+}
+
+__device__ __forceinline__ float biased_code_of(float value, float scale) {
+    return biased_code(__fdiv_rn(value, scale));
+}
+
+// The code as an integer-valued float (for decode = code * scale).
+__device__ __forceinline__ float code_value(float biased) {
+    return __fadd_rn(biased, -kRoundMagic);
+}
+
+__device__ __forceinline__ signed char code_byte(float biased) {
+    return static_cast<signed char>(__float_as_uint(biased) & 0xffu);
+}
+
+// Four biased codes -> four int8 in one word (element 0 in the low byte).
+__device__ __forceinline__ unsigned pack_codes(float t0, float t1, float t2, float t3) {
+    unsigned lo = __byte_perm(__float_as_uint(t0), __float_as_uint(t1), 0x0040);
+    unsigned hi = __byte_perm(__float_as_uint(t2), __float_as_uint(t3), 0x0040);
+    return __byte_perm(lo, hi, 0x5410);
+}
+
+// int8 byte `index` of `word` -> float, exactly, on the integer/FP32 pipes
+// only: (byte ^ 0x80) placed in the mantissa of 2^23 * 1.5 and the bias
+// subtracted.  `biased` must already be word ^ 0x80808080.
+__device__ __forceinline__ float byte_to_float(unsigned biased, int index) {
+    unsigned bits = __byte_perm(biased, 0x4B400000u, 0x7650 + index);   // 0x4B4000bb
+    return __fadd_rn(__uint_as_float(bits), -12583040.0f);              // -(1.5*2^23 + 128)
+}
+
+__device__ __forceinline__ bool is_non_finite(float v) {
+    return (__float_as_uint(v) & 0x7fffffffu) >= 0x7f800000u;
+}
+
+__device__ __forceinline__ float4 load_f4(const float* p) {
+    return *reinterpret_cast<const float4*>(p);
+}
+// Streaming load: read once, do not keep in L1.
+__device__ __forceinline__ float4 load_f4_stream(const float* p) {
+    return __ldcs(reinterpret_cast<const float4*>(p));
+}
+__device__ __forceinline__ void store_f4(float* p, float4 v) {
+    *reinterpret_cast<float4*>(p) = v;
+}
+
+__device__ __forceinline__ double warp_sum(double v) {
+    #pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1)
+        v += __shfl_xor_sync(0xffffffffu, v, offset);
+    return v;
+}
+
+// Adds every thread's `partial` into *target with one atomic per CTA.
+// Must be reached by all threads of the CTA.
+__device__ __forceinline__ void cta_accumulate(double partial, double* target) {
+    __shared__ double warp_partials[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    partial = warp_sum(partial);
+    if (lane == 0) warp_partials[warp] = partial;
+    __syncthreads();
+    if (warp == 0) {
+        const int warps = (blockDim.x + 31) >> 5;
+        double v = lane < warps ? warp_partials[lane] : 0.0;
+        v = warp_sum(v);
+        if (lane == 0 && v != 0.0) atomicAdd(target, v);
+    }
+}
+
+// Same, but the CTA's total goes to partials[blockIdx.x] (no atomics), for a
+// fixed-order second stage.
+__device__ __forceinline__ void cta_store_partial(double partial, double* partials) {
+    __shared__ double warp_partials_det[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    partial = warp_sum(partial);
+    if (lane == 0) warp_partials_det[warp] = partial;
+    __syncthreads();
+    if (warp == 0) {
+        const int warps = (blockDim.x + 31) >> 5;
+        double v = lane < warps ? warp_partials_det[lane] : 0.0;
+        v = warp_sum(v);
+        if (lane == 0) partials[blockIdx.x] = v;
+    }
+}
+
+#endif  // __CUDACC__
+
+}  // namespace ngb

@@ -1,0 +1,134 @@
+// Host-side launchers for the reduction kernels in reduce_kernels.cuh.
+#include "reduce_kernels.cuh"
+
+namespace ngb {
+namespace {
+
+inline bool aligned_to(const void* p, std::uintptr_t bytes) {
+    return (reinterpret_cast<std::uintptr_t>(p) & (bytes - 1)) == 0;
+}
+
+template <int kBlock, int kRanks>
+cudaError_t run_reencode(const EncodedShards& shards, long long first_value, long long end_value,
+                         float reduction_scale, double* squared_sum, int* finite_status,
+                         bool vector_ok, cudaStream_t stream) {
+    const long long tiles = (end_value - first_value + 511) / 512;
+    const int grid = grid_for((tiles + kWarpsPerCta - 1) / kWarpsPerCta, kCtasPerSm);
+    if (squared_sum != nullptr) {
+        bfp8_reduce_reencode_kernel<kBlock, kRanks, true><<<grid, kThreads, 0, stream>>>(
+            shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok);
+    } else {
+        bfp8_reduce_reencode_kernel<kBlock, kRanks, false><<<grid, kThreads, 0, stream>>>(
+            shards, first_value, end_value, reduction_scale, nullptr, finite_status, vector_ok);
+    }
+    return cudaPeekAtLastError();
+}
+
+template <int kBlock>
+cudaError_t dispatch_reencode(const EncodedShards& shards, long long first_value, long long end_value,
+                              float reduction_scale, double* squared_sum, int* finite_status,
+                              bool vector_ok, cudaStream_t stream) {
+    switch (shards.inputs) {
+        case 2: return run_reencode<kBlock, 2>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, stream);
+        case 4: return run_reencode<kBlock, 4>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, stream);
+        case 8: return run_reencode<kBlock, 8>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, stream);
+        default: return run_reencode<kBlock, 0>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, stream);
+    }
+}
+
+template <int kShift, bool kGuard, bool kSquares, bool kMaximum>
+void run_sum(int grid, cudaStream_t stream, const EncodedInputs& in, float* reduced, long long length,
+             long long block, float reduction_scale, double* squared_sum, int* finite_status,
+             unsigned* maximum_bits, bool vector_ok) {
+    bfp8_sum_to_f32_kernel<kShift, kGuard, kSquares, kMaximum><<<grid, kThreads, 0, stream>>>(
+        in, reduced, length, block, reduction_scale, squared_sum, finite_status, maximum_bits, vector_ok);
+}
+
+template <int kShift>
+void dispatch_sum(int grid, cudaStream_t stream, const EncodedInputs& in, float* reduced, long long length,
+                  long long block, float reduction_scale, double* squared_sum, int* finite_status,
+                  unsigned* maximum_bits, bool vector_ok) {
+    const int key = (finite_status ? 4 : 0) | (squared_sum ? 2 : 0) | (maximum_bits ? 1 : 0);
+#define NGB_SUM(K, G, S, M) \
+    case K: run_sum<kShift, G, S, M>(grid, stream, in, reduced, length, block, reduction_scale, squared_sum, finite_status, maximum_bits, vector_ok); break;
+    switch (key) {
+        NGB_SUM(0, false, false, false) NGB_SUM(1, false, false, true)
+        NGB_SUM(2, false, true, false) NGB_SUM(3, false, true, true)
+        NGB_SUM(4, true, false, false) NGB_SUM(5, true, false, true)
+        NGB_SUM(6, true, true, false) NGB_SUM(7, true, true, true)
+    }
+#undef NGB_SUM
+}
+
+}  // namespace
+
+cudaError_t launch_bfp8_reduce_reencode(const EncodedShards& shards, long long first_value,
+                                        long long end_value, int block, float reduction_scale,
+                                        double* squared_sum, int* finite_status, cudaStream_t stream) {
+    if (shards.inputs < 1 || shards.inputs > kMaxRanks || shards.outputs < 1 || shards.outputs > kMaxRanks)
+        return cudaErrorInvalidValue;
+    if (first_value < 0 || end_value <= first_value) return cudaErrorInvalidValue;
+    if (block != 32 && block != 64 && block != 128) return cudaErrorInvalidValue;
+    if (first_value % block != 0) return cudaErrorInvalidValue;
+    bool vector_ok = first_value % 16 == 0;
+    for (int k = 0; k < shards.inputs; ++k) {
+        if (!shards.payload[k] || !shards.scales[k]) return cudaErrorInvalidValue;
+        vector_ok = vector_ok && aligned_to(shards.payload[k], 16);
+    }
+    for (int d = 0; d < shards.outputs; ++d) {
+        if (!shards.out_payload[d] || !shards.out_scales[d]) return cudaErrorInvalidValue;
+        vector_ok = vector_ok && aligned_to(shards.out_payload[d], 16);
+    }
+    switch (block) {
+        case 32: return dispatch_reencode<32>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, stream);
+        case 64: return dispatch_reencode<64>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, stream);
+        default: return dispatch_reencode<128>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, stream);
+    }
+}
+
+cudaError_t launch_bfp8_sum_to_f32(const EncodedInputs& in, float* reduced, long long length,
+                                   long long block, float reduction_scale, double* squared_sum,
+                                   int* finite_status, unsigned* maximum_bits, cudaStream_t stream) {
+    if (in.inputs < 1 || in.inputs > kMaxRanks || !reduced || length <= 0 || block <= 0)
+        return cudaErrorInvalidValue;
+    if (block > length) block = length;
+    bool vector_ok = aligned_to(reduced, 16);
+    for (int k = 0; k < in.inputs; ++k) {
+        if (!in.payload[k] || !in.scales[k]) return cudaErrorInvalidValue;
+        vector_ok = vector_ok && aligned_to(in.payload[k], 4);
+    }
+    const int grid = grid_for((length / 4 + kThreads - 1) / kThreads, kCtasPerSm);
+    if (block == 32) dispatch_sum<5>(grid, stream, in, reduced, length, block, reduction_scale, squared_sum, finite_status, maximum_bits, vector_ok);
+    else if (block == 128) dispatch_sum<7>(grid, stream, in, reduced, length, block, reduction_scale, squared_sum, finite_status, maximum_bits, vector_ok);
+    else dispatch_sum<-1>(grid, stream, in, reduced, length, block, reduction_scale, squared_sum, finite_status, maximum_bits, vector_ok);
+    return cudaPeekAtLastError();
+}
+
+cudaError_t launch_bf16_reduce(const Bf16Inputs& io, float* reduced, long long first_value,
+                               long long end_value, float reduction_scale, double* squared_sum,
+                               bool square_of_bf16, cudaStream_t stream) {
+    if (io.inputs < 1 || io.inputs > kMaxRanks || io.outputs < 0 || io.outputs > kMaxRanks)
+        return cudaErrorInvalidValue;
+    if (first_value < 0 || end_value <= first_value || (!reduced && io.outputs == 0 && !squared_sum))
+        return cudaErrorInvalidValue;
+    bool vector_ok = first_value % 8 == 0 && (!reduced || aligned_to(reduced, 16));
+    for (int k = 0; k < io.inputs; ++k) {
+        if (!io.values[k]) return cudaErrorInvalidValue;
+        vector_ok = vector_ok && aligned_to(io.values[k], 16);
+    }
+    for (int d = 0; d < io.outputs; ++d) {
+        if (!io.out_bf16[d]) return cudaErrorInvalidValue;
+        vector_ok = vector_ok && aligned_to(io.out_bf16[d], 16);
+    }
+    const long long groups = (end_value - first_value + 7) / 8;
+    const int grid = grid_for((groups + kThreads - 1) / kThreads, kCtasPerSm);
+    if (!squared_sum)
+        bf16_reduce_kernel<false, false><<<grid, kThreads, 0, stream>>>(io, reduced, first_value, end_value, reduction_scale, nullptr, vector_ok);
+    else if (square_of_bf16)
+        bf16_reduce_kernel<true, true><<<grid, kThreads, 0, stream>>>(io, reduced, first_value, end_value, reduction_scale, squared_sum, vector_ok);
+    else
+        bf16_reduce_kernel<true, false><<<grid, kThreads, 0, stream>>>(io, reduced, first_value, end_value, reduction_scale, squared_sum, vector_ok);
+    return cudaPeekAtLastError();
+}
+
+}  // namespace ngb

@@ -1,0 +1,37 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    import oracle as module
+    module.build()
+    return module
+
+
+@pytest.fixture(scope="session")
+def lib():
+    from nntrain_b200 import build as builder
+    from nntrain_b200.library import load
+    if not os.path.exists(builder.LIBRARY):
+        builder.build()
+    return load()
+
+
+@pytest.fixture(scope="session")
+def cuda():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.fail("a test marked gpu ran without a CUDA device")
+    torch.cuda.set_device(0)
+    return torch

@@ -1,0 +1,410 @@
+#!/usr/bin/env python
+"""Benchmark of the compressed data-parallel gradient path.
+
+    python bench.py --gpus N --steps K --warmup W          (N = 1)
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N \\
+        --master-addr 127.0.0.1 --master-port P bench.py --gpus N --steps K --warmup W
+
+One step = one BFP8 (block 32) all-reduce of the whole fp32 gradient arena of
+the workload on every rank: encode, reduce-scatter + fp32 accumulate in rank
+order + re-encode + all-gather, decode back into the fp32 arena, fused global
+L2 clip-norm (max_norm 1.0, scale-only).  At N = 1 the collective is absent
+and the step is the single-GPU publication: encode with fused decode
+write-back, sum of squares and finite flag, then the clip.
+
+Workload: the gradient arena of a Qwen2-1.5B-shaped model (1,543,714,304 fp32
+values per rank, weak scaling: every rank holds a full replica's gradient),
+synthetic N(0, sigma) with sigma log-uniform in [1e-5, 1e-2] per 65,536-value
+slice, 1 % of 32-value blocks x100, 0.5 % all-zero blocks.
+
+Rank 0 prints one JSON line.  `value` = N * 4 * E / t: fp32-equivalent
+gradient bytes reduced per second summed over the ranks (the per-rank
+all-reduce "algorithm bandwidth" 4E/t is `algbw_gbs`; wire bytes per rank per
+direction over time is `busbw_gbs`).  `--impl reference` times the CPU
+restatement of the reference's codec and reducer on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+QWEN2_1P5B_ELEMENTS = 1_543_714_304
+BLOCK = 32
+MAX_NORM = 1.0
+METRIC = "bfp8_grad_allreduce_fp32_equiv_gbs"
+UNIT = "GB/s"
+NVLINK_PER_DIRECTION_GBS = 900.0          # nominal, per GPU per direction
+NVLINK_MEASURED_PEER_COPY_GBS = 770.0     # measured peer copy on this pool
+# DRAM bytes per value of the dominant kernel (encode + write-back + sum of
+# squares) from the ncu capture summarised in
+# profiles/bfp8_encode_block32_publish_64Mi.md; None until captured.
+ENCODE_PUBLISH_DRAM_BYTES_PER_VALUE = None
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=10)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", choices=("b200", "reference"), default="b200")
+    p.add_argument("--elements", type=int, default=QWEN2_1P5B_ELEMENTS)
+    p.add_argument("--mode", choices=("peer", "nccl"), default="peer")
+    p.add_argument("--chunk-elements", type=int, default=0, help="0 = pick by world size")
+    p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--cpu-sample-elements", type=int, default=64 << 20)
+    return p.parse_args()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            data = json.load(f)
+        return float(data["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ---- clocks -------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi while the timed region runs (reading only)."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.rows = []
+        self.process = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.process = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.process.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, begin: float, end: float):
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.process.terminate()
+        try:
+            self.process.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+        rows = [r for t, r in self.rows if begin <= t <= end] or [r for _, r in self.rows]
+        clocks, maxima, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                clocks.append(float(r[1]))
+                maxima.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, cell in zip(names, r[5:9]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None,
+                "sm_max_mhz": max(maxima) if maxima else None, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+# ---- synthetic gradient on the device -------------------------------------------------
+def fill_gradient(arena, seed: int, rank: int):
+    """Configuration 0's distribution, generated on the device in slices."""
+    import torch
+    n = arena.numel()
+    generator = torch.Generator(device=arena.device)
+    generator.manual_seed(seed * 1000003 + rank)
+    slice_elements = 65536
+    piece = 1 << 26
+    for start in range(0, n, piece):
+        stop = min(start + piece, n)
+        view = arena[start:stop]
+        view.normal_(generator=generator)
+        slices = (stop - start + slice_elements - 1) // slice_elements
+        exponents = torch.rand(slices, device=arena.device, generator=generator) * 3.0 - 5.0
+        sigma = torch.pow(10.0, exponents).repeat_interleave(slice_elements)[:stop - start]
+        view.mul_(sigma)
+        blocks = (stop - start) // 32
+        if blocks:
+            kind = torch.rand(blocks, device=arena.device, generator=generator)
+            factor = torch.ones(blocks, device=arena.device)
+            factor[kind < 0.005] = 0.0
+            factor[(kind >= 0.005) & (kind < 0.015)] = 100.0
+            view[:blocks * 32].view(blocks, 32).mul_(factor.unsqueeze(1))
+        del sigma, exponents
+
+
+# ---- CPU baseline (the oracle port, checker code timed as the baseline) ---------------
+def cpu_baseline(world: int, sample_elements: int, budget_seconds: float = 12.0):
+    import numpy as np
+    import oracle
+    oracle.build()
+    threads = oracle.max_threads()
+    oracle.set_threads(threads)
+    replicas = [oracle.generate_gradient(sample_elements, 0xB2000004, r) for r in range(world)]
+
+    def one_pass():
+        if world == 1:
+            oracle.gradient_publish(replicas[0], BLOCK)
+        else:
+            oracle.allreduce_bfp8(replicas, BLOCK, 1.0 / world)
+
+    one_pass()                      # warm-up
+    times = []
+    begin = time.perf_counter()
+    while len(times) < 3 or (time.perf_counter() - begin < budget_seconds and len(times) < 50):
+        t0 = time.perf_counter()
+        one_pass()
+        times.append(time.perf_counter() - t0)
+    best = min(times)
+    del np
+    return {"value": world * 4.0 * sample_elements / best / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{sample_elements} fp32 values per replica x {world} replica(s), best of {len(times)} "
+                      f"passes of encode(block 32)" + (" + decode write-back + sum of squares"
+                                                       if world == 1 else
+                                                       " x N + rank-ordered fp32 sum + re-encode + decode + sum of squares"),
+            "seconds_per_pass": best}
+
+
+def run_reference_arm(args, rank: int, world: int):
+    """The reference's CPU implementation of the path (restated in C, see
+    oracle/), all host threads, on a bounded sample of the same workload."""
+    if rank != 0:
+        return
+    import oracle
+    oracle.build()
+    threads = oracle.max_threads()
+    oracle.set_threads(threads)
+    sample = min(args.cpu_sample_elements, args.elements)
+    replicas = [oracle.generate_gradient(sample, 0xB2000004, r) for r in range(world)]
+
+    def one_step():
+        if world == 1:
+            _, _, scales, _, sq = oracle.gradient_publish(replicas[0], BLOCK)
+        else:
+            _, scales, _, sq = oracle.allreduce_bfp8(replicas, BLOCK, 1.0 / world)
+        _, c = oracle.clip_coefficient(sq, MAX_NORM)
+        oracle.scale_bfp8_scales(scales, c)
+
+    for _ in range(args.warmup):
+        one_step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        one_step()
+    elapsed = time.perf_counter() - t0
+    ms = elapsed / args.steps * 1e3
+    value = world * 4.0 * sample / (elapsed / args.steps) / 1e9
+    sample_text = (f"{sample} of {args.elements} fp32 values per replica x {world} replica(s) per step "
+                   f"(CPU restatement of the reference codec/reducer, OpenMP over blocks)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "qwen2-1.5b gradient arena, BFP8 block-32 all-reduce + clip-norm (CPU sample)",
+                   "elements_per_rank": args.elements, "block": BLOCK, "max_norm": MAX_NORM,
+                   "sample_elements": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample_text},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        print(f"--gpus {args.gpus} needs torch.distributed.run with --nproc-per-node {args.gpus}", file=sys.stderr)
+        sys.exit(2)
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from nntrain_b200 import reducers
+    from nntrain_b200.library import load
+    load()      # fails loudly when the CUDA library is missing
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("cpu:gloo,cuda:nccl", device_id=device)
+
+    E = args.elements
+    mode = reducers.PEER if args.mode == "peer" else reducers.NCCL
+    chunk = args.chunk_elements or (0 if world == 1 else 128 << 20)
+    group = reducers.GradientGroup(world, rank, local_rank)
+    step = reducers.Bfp8ArenaAllReduce(group, E, BLOCK, mode, chunk_elements=chunk or None,
+                                       reduction_scale=1.0 / world, write_fp32=True)
+    arena = torch.empty(E, dtype=torch.float32, device=device)
+    fill_gradient(arena, 0xB2000004, rank)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    # -- device-resident timing -----------------------------------------------------
+    for _ in range(args.warmup):
+        step.enqueue(arena, MAX_NORM)
+    result = step.complete(MAX_NORM)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    wall_begin = time.time()
+    begin.record()
+    for _ in range(args.steps):
+        step.enqueue(arena, MAX_NORM)
+    end.record()
+    torch.cuda.synchronize()
+    barrier()
+    wall_end = time.time()
+    result = step.complete(MAX_NORM)
+    elapsed_ms = begin.elapsed_time(end)
+    clocks = sampler.stop(wall_begin, wall_end) if rank == 0 else None
+    launches = step.kernel_launches * args.steps
+
+    # -- dominant kernel, timed alone on its stream -------------------------------------
+    from nntrain_b200.native import CudaBfp8Native
+    kernel_begin, kernel_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sq = torch.zeros(1, dtype=torch.float64, device=device)
+    flag = torch.zeros(1, dtype=torch.int32, device=device)
+    kernel_runs = max(3, min(args.steps, 10))
+    publish = world == 1
+    for timed in (False, True):
+        if timed:
+            kernel_begin.record()
+        for _ in range(kernel_runs if timed else 2):
+            if publish:
+                CudaBfp8Native.block_encode(local_rank, arena, step.payload, step.scales, BLOCK, roundtrip=arena,
+                                            squared_sum=sq, finite_status=flag)
+            else:
+                CudaBfp8Native.block_encode(local_rank, arena, step.payload, step.scales, BLOCK,
+                                            finite_status=flag)
+        if timed:
+            kernel_end.record()
+    torch.cuda.synchronize()
+    kernel_ms = kernel_begin.elapsed_time(kernel_end) / kernel_runs
+    bytes_per_value = (9.125 if publish else 5.125)
+    hbm_peak, peak_kind = measured_peaks()
+    achieved = bytes_per_value * E / (kernel_ms * 1e-3) / 1e9
+    traffic = (ENCODE_PUBLISH_DRAM_BYTES_PER_VALUE * E
+               if (ENCODE_PUBLISH_DRAM_BYTES_PER_VALUE is not None and publish) else None)
+    roofline = {"bound": "hbm", "kernel": "bfp8_encode_blocks_kernel<32>" + (" publish" if publish else ""),
+                "achieved": achieved, "peak": hbm_peak, "peak_kind": peak_kind, "unit": "GB/s",
+                "frac": achieved / hbm_peak, "traffic": traffic, "algorithmic_bytes": bytes_per_value * E,
+                "ms_per_launch": kernel_ms}
+
+    # -- end to end: pinned host buffers in, encoded result out -----------------------------
+    e2e = None
+    if not args.no_e2e:
+        host_gradient = torch.empty(E, dtype=torch.float32).pin_memory()
+        host_payload = torch.empty(E, dtype=torch.int8).pin_memory()
+        host_scales = torch.empty(step.scale_count, dtype=torch.float32).pin_memory()
+        host_gradient.copy_(arena)
+        e2e_chunk = 64 << 20
+        e2e_step = step if (step.chunk <= e2e_chunk) else None
+        if e2e_step is None:
+            step.close()
+            e2e_step = reducers.Bfp8ArenaAllReduce(group, E, BLOCK, mode, chunk_elements=e2e_chunk,
+                                                   reduction_scale=1.0 / world, write_fp32=True)
+        e2e_steps = max(1, min(args.steps, 5))
+        for _ in range(min(args.warmup, 2)):
+            e2e_step.enqueue(arena, MAX_NORM, host_gradient, host_payload, host_scales)
+        barrier()
+        torch.cuda.synchronize()
+        b2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b2.record()
+        for _ in range(e2e_steps):
+            e2e_step.enqueue(arena, MAX_NORM, host_gradient, host_payload, host_scales)
+            e2e_result = e2e_step.complete(MAX_NORM)       # the host reads the step's result
+        e2.record()
+        torch.cuda.synchronize()
+        barrier()
+        e2e_ms = b2.elapsed_time(e2) / e2e_steps
+        if world > 1:
+            t = torch.tensor([e2e_ms], dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
+        e2e = {"value": world * 4.0 * E / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+               "h2d_bytes_per_step": 4 * E, "d2h_bytes_per_step": E + 4 * step.scale_count + 24,
+               "ms_per_step": e2e_ms, "steps": e2e_steps,
+               "path": "Bfp8ArenaAllReduce.enqueue(host buffers) + complete(), per step"}
+        step = e2e_step
+        del host_gradient, host_payload, host_scales
+
+    if world > 1:
+        t = torch.tensor([elapsed_ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    seconds = ms_per_step * 1e-3
+    algbw = 4.0 * E / seconds / 1e9
+    wire_bytes = 2 * (world - 1) / world * (E + 4 * step.scale_count)
+    busbw = wire_bytes / seconds / 1e9
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(world, min(args.cpu_sample_elements, E))
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": world * algbw, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "qwen2-1.5b gradient arena, BFP8 block-32 all-reduce + decode + clip-norm",
+                       "elements_per_rank": E, "block": BLOCK, "max_norm": MAX_NORM,
+                       "transport": args.mode if world > 1 else "none (single-GPU publication)",
+                       "chunk_elements": step.chunk, "reduction": "mean (reduction_scale 1/N)",
+                       "l2": "inputs (6.2 GB per rank) exceed the 126 MB L2; no flush needed",
+                       "fp32_result": "arena overwritten with decode(encode(sum)) every step"},
+            "algbw_gbs": algbw, "busbw_gbs": busbw,
+            "nvlink": None if world == 1 else {
+                "wire_bytes_per_rank_per_direction": wire_bytes, "achieved": busbw,
+                "peak_nominal": NVLINK_PER_DIRECTION_GBS, "frac_nominal": busbw / NVLINK_PER_DIRECTION_GBS,
+                "peak_measured_peer_copy": NVLINK_MEASURED_PEER_COPY_GBS,
+                "frac_measured": busbw / NVLINK_MEASURED_PEER_COPY_GBS, "unit": "GB/s"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks,
+            "result": {"norm": result.norm, "clip_coefficient": result.coefficient, "finite": result.finite},
+        }
+        print(json.dumps(line), flush=True)
+    step.close()
+    group.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -222,6 +222,66 @@ int nntrain_gradient_clip_coefficient(int device, const double* squared_sum, flo
 int nntrain_gradient_clip_apply(int device, int kind, void* values, long long count, float multiplier,
                                 const float* coefficient, nntrain_stream_t stream);
 
+/* ---- N-rank all-reduce, one process per GPU (ABI minor 36) -------------------
+ * The reference's compressed reducers accept exactly two devices of one
+ * process (NNtrain.Core/Training/CudaBfp8GradientAllReduce.cs:44-49,
+ * CudaBFloat16GradientAllReduce.cs:119-124); these carry the same arithmetic,
+ * summed left to right over ranks 0..N-1, to N ranks.  Status values of
+ * 10000 + n are NCCL results (10099: NCCL could not be loaded). */
+
+/* Peer-visible device memory (CUDA IPC): cudaMalloc + the 64-byte handle
+ * other processes map. */
+int nntrain_gradient_peer_alloc(int device, long long bytes, void** pointer, void* handle64);
+/* Frees memory from nntrain_gradient_peer_alloc. */
+int nntrain_gradient_peer_free(int device, void* pointer);
+/* Maps a peer's handle into this process (peer access enabled lazily). */
+int nntrain_gradient_peer_open(int device, const void* handle64, void** pointer);
+/* Unmaps a pointer from nntrain_gradient_peer_open. */
+int nntrain_gradient_peer_close(int device, void* pointer);
+/* 128-byte NCCL unique id (rank 0 creates, host distributes). */
+int nntrain_gradient_group_unique_id(void* id128);
+/* Collective.  world == 1 needs neither an id nor NCCL. */
+int nntrain_gradient_group_create(const void* id128, int world, int rank, int device, void** group);
+/* Destroys the communicator and the group's device scratch. */
+int nntrain_gradient_group_destroy(void* group);
+/* Host-side liveness: 0 or the communicator's asynchronous error; never blocks. */
+int nntrain_gradient_group_poll(void* group);
+/* Abandon the communicator without waiting (a peer was declared lost). */
+int nntrain_gradient_group_abort(void* group);
+/* In-place sum of `count` doubles over the ranks; count 0 = barrier. */
+int nntrain_gradient_group_sum(void* group, double* values, int count, nntrain_stream_t stream);
+/* Shard `rank` of an arena of `length` values: contiguous, 512-value aligned. */
+int nntrain_gradient_shard_range(long long length, int world, int rank, long long* first, long long* end);
+/* Owner arithmetic on host tables of device pointers (local or peer):
+ * r = reduction_scale * (rank-ordered fp32 sum of decoded inputs) over
+ * [first_value, end_value), re-encoded (block 32/64/128), stored to every
+ * output; optional sum of squares of the decoded result and finite flag.
+ * Extends NNtrain.Cuda/native/tensor_kernels.cu:1084-1106 + 1114-1146. */
+int nntrain_gradient_reduce_shards_bfp8(
+    int device, int inputs, const signed char* const* payloads, const float* const* scales, int outputs,
+    signed char* const* out_payloads, float* const* out_scales, long long first_value,
+    long long end_value, int block_size, float reduction_scale, double* squared_sum,
+    int* finite_status, nntrain_stream_t stream);
+/* bf16 twin (extends NNtrain.Cuda/native/gradient_collectives.cu:62-90). */
+int nntrain_gradient_reduce_shards_bf16(
+    int device, int inputs, const unsigned short* const* values, int outputs,
+    unsigned short* const* out_values, float* reduced, long long first_value, long long end_value,
+    float reduction_scale, double* squared_sum, int square_of_bf16, nntrain_stream_t stream);
+/* In-place BFP8 all-reduce of an encoded arena (or one chunk of it).
+ * mode 0: peer memory, one fused reduce-scatter + accumulate + re-encode +
+ * all-gather kernel; mode 1: NCCL send/recv through staging (world shards).
+ * phase: bit 0 = first chunk of a step, bit 1 = last chunk (fence, sum of
+ * squares and finite flag summed over ranks and published); 3 = whole arena. */
+int nntrain_gradient_allreduce_bfp8(
+    void* group, signed char* const* payload_by_rank, float* const* scales_by_rank, long long length,
+    int block_size, float reduction_scale, double* squared_sum, int* finite_status, int mode,
+    int phase, signed char* staging_payload, float* staging_scales, nntrain_stream_t stream);
+/* In-place bf16 arena all-reduce (fp32 accumulate, bf16 result); mode and
+ * phase as above. */
+int nntrain_gradient_allreduce_bf16(
+    void* group, unsigned short* const* values_by_rank, long long length, float reduction_scale,
+    double* squared_sum, int mode, int phase, unsigned short* staging, nntrain_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

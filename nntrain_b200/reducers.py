@@ -1,0 +1,388 @@
+"""N-rank gradient-arena reducers: the host side of the all-reduce, one
+process per GPU.
+
+The reference's reducers (`CudaBfp8GradientAllReducePlan`,
+NNtrain.Core/Training/CudaBfp8GradientAllReduce.cs:9-841, and
+`CudaBFloat16GradientAllReducePlan`, CudaBFloat16GradientAllReduce.cs:47-1866)
+live in one process, drive two devices from two threads and move whole
+buckets with peer copies.  Here every rank is a process; the encoded arena of
+each rank sits in peer-visible memory, and one call of the C ABI performs the
+reduce-scatter, the owner's fp32 accumulate + re-encode and the all-gather.
+`torch.distributed` is used only to hand out the NCCL id and the IPC handles.
+
+Arena layout is the reference's (CudaBFloat16GradientAllReduce.cs:1515-1601):
+one contiguous fp32 gradient arena per bucket with parameters at running-sum
+offsets, an int8 payload sidecar of the same element layout and one fp32
+scale per block, blocks running over the bucket (not per tensor).
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from .library import check, load
+from .native import CudaBfp8Native, GradientNorm, _stream
+
+PEER, NCCL = 0, 1
+
+
+def shard_range(length: int, world: int, rank: int) -> tuple[int, int]:
+    first, end = ctypes.c_longlong(), ctypes.c_longlong()
+    check("gradient_shard_range", load().nntrain_gradient_shard_range(
+        length, world, rank, ctypes.addressof(first), ctypes.addressof(end)))
+    return first.value, end.value
+
+
+def _pointer_table(pointers):
+    return (ctypes.c_void_p * len(pointers))(*pointers)
+
+
+def reduce_shards_bfp8(device: int, payloads, scales, out_payloads, out_scales, first: int, end: int,
+                       block_size: int, reduction_scale: float = 1.0, squared_sum=None, finite_status=None,
+                       stream=None) -> None:
+    """Owner arithmetic on explicit tensors (each list entry one rank's arena)."""
+    check("gradient_reduce_shards_bfp8", load().nntrain_gradient_reduce_shards_bfp8(
+        device, len(payloads), _pointer_table([t.data_ptr() for t in payloads]),
+        _pointer_table([t.data_ptr() for t in scales]), len(out_payloads),
+        _pointer_table([t.data_ptr() for t in out_payloads]),
+        _pointer_table([t.data_ptr() for t in out_scales]), first, end, block_size, reduction_scale,
+        0 if squared_sum is None else squared_sum.data_ptr(),
+        0 if finite_status is None else finite_status.data_ptr(), _stream(stream)))
+
+
+def reduce_shards_bf16(device: int, values, out_values, reduced, first: int, end: int,
+                       reduction_scale: float = 1.0, squared_sum=None, square_of_bf16: bool = True,
+                       stream=None) -> None:
+    check("gradient_reduce_shards_bf16", load().nntrain_gradient_reduce_shards_bf16(
+        device, len(values), _pointer_table([t.data_ptr() for t in values]), len(out_values),
+        _pointer_table([t.data_ptr() for t in out_values]) if out_values else None,
+        0 if reduced is None else reduced.data_ptr(), first, end, reduction_scale,
+        0 if squared_sum is None else squared_sum.data_ptr(), int(square_of_bf16), _stream(stream)))
+
+
+class GradientGroup:
+    """This rank's membership of the job (world, rank, device, communicator)."""
+
+    def __init__(self, world: int = 1, rank: int = 0, device: int = 0, process_group=None):
+        self.world, self.rank, self.device = world, rank, device
+        self.process_group = process_group
+        lib = load()
+        identifier = None
+        if world > 1:
+            import torch.distributed as dist
+            holder = [None]
+            if rank == 0:
+                buffer = ctypes.create_string_buffer(128)
+                check("gradient_group_unique_id", lib.nntrain_gradient_group_unique_id(buffer))
+                holder[0] = buffer.raw
+            dist.broadcast_object_list(holder, src=0, group=process_group)
+            identifier = ctypes.create_string_buffer(holder[0], 128)
+        handle = ctypes.c_void_p()
+        check("gradient_group_create", lib.nntrain_gradient_group_create(
+            identifier, world, rank, device, ctypes.addressof(handle)))
+        self.handle = handle.value
+
+    def poll(self) -> int:
+        return load().nntrain_gradient_group_poll(self.handle)
+
+    def sum(self, values: torch.Tensor, stream=None) -> None:
+        check("gradient_group_sum", load().nntrain_gradient_group_sum(
+            self.handle, values.data_ptr(), values.numel(), _stream(stream)))
+
+    def barrier(self, stream=None) -> None:
+        check("gradient_group_sum", load().nntrain_gradient_group_sum(self.handle, None, 0, _stream(stream)))
+
+    def close(self) -> None:
+        if self.handle:
+            check("gradient_group_destroy", load().nntrain_gradient_group_destroy(self.handle))
+            self.handle = None
+
+
+class PeerBuffer:
+    """`nbytes` of device memory every rank of the group can address.
+
+    `pointers[k]` is rank k's buffer as mapped in this process; `tensor(dtype)`
+    views this rank's own buffer as a torch tensor (no copy)."""
+
+    def __init__(self, group: GradientGroup, nbytes: int):
+        self.group, self.nbytes = group, nbytes
+        lib = load()
+        pointer = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        check("gradient_peer_alloc", lib.nntrain_gradient_peer_alloc(
+            group.device, nbytes, ctypes.addressof(pointer), handle))
+        self.local = pointer.value
+        self.pointers = [None] * group.world
+        self.pointers[group.rank] = self.local
+        self._opened = []
+        if group.world > 1:
+            import torch.distributed as dist
+            handles = [None] * group.world
+            dist.all_gather_object(handles, handle.raw, group=group.process_group)
+            for k, raw in enumerate(handles):
+                if k == group.rank:
+                    continue
+                mapped = ctypes.c_void_p()
+                check("gradient_peer_open", lib.nntrain_gradient_peer_open(
+                    group.device, ctypes.create_string_buffer(raw, 64), ctypes.addressof(mapped)))
+                self.pointers[k] = mapped.value
+                self._opened.append(mapped.value)
+
+    def tensor(self, dtype: torch.dtype, count: int | None = None) -> torch.Tensor:
+        itemsize = torch.empty((), dtype=dtype).element_size()
+        count = self.nbytes // itemsize if count is None else count
+        return _device_view(self.local, count, dtype, self.group.device)
+
+    def close(self) -> None:
+        lib = load()
+        if self.group.world > 1:
+            import torch.distributed as dist
+            torch.cuda.synchronize(self.group.device)
+            dist.barrier(group=self.group.process_group)
+        for mapped in self._opened:
+            lib.nntrain_gradient_peer_close(self.group.device, mapped)
+        self._opened = []
+        if self.group.world > 1:
+            import torch.distributed as dist
+            dist.barrier(group=self.group.process_group)
+        if self.local:
+            lib.nntrain_gradient_peer_free(self.group.device, self.local)
+            self.local = None
+
+
+class _CudaArrayInterface:
+    def __init__(self, pointer: int, count: int, typestr: str):
+        self.__cuda_array_interface__ = {"shape": (count,), "typestr": typestr, "data": (pointer, False),
+                                         "version": 3, "strides": None}
+
+
+_TYPESTR = {torch.int8: "|i1", torch.float32: "<f4", torch.int16: "<i2", torch.float64: "<f8",
+            torch.int32: "<i4", torch.uint8: "|u1"}
+
+
+def _device_view(pointer: int, count: int, dtype: torch.dtype, device: int) -> torch.Tensor:
+    """A torch tensor over memory the library allocated (zero-copy)."""
+    with torch.cuda.device(device):
+        return torch.as_tensor(_CudaArrayInterface(pointer, count, _TYPESTR[dtype]), device=f"cuda:{device}")
+
+
+@dataclass
+class StepResult:
+    norm: float            # global L2 norm before clipping
+    coefficient: float     # clip multiplier that was applied (1.0 = none)
+    squared_sum: float
+    finite: bool
+
+
+class Bfp8ArenaAllReduce:
+    """BFP8 all-reduce of one fp32 gradient arena across the group, with the
+    fused global clip-norm.
+
+    Per step (everything enqueued on streams, one host read at the end):
+      encode     fp32 arena -> payload + scales           (compute stream)
+      all-reduce in place over the encoded arena          (communication stream)
+      decode     reduced payload -> fp32 arena            (optional; the fp32
+                 arena then holds decode(encode(sum)), the reference's decode
+                 cache, NNtrain.Cuda/native/tensor_kernels.cu:3988-3997,4034-4036)
+      clip       scale-only, coefficient computed on the device from the fused
+                 sum of squares (NNtrain.Core/Tensors/Tensor.CudaKernels.cs:321-437)
+    The arena is processed in `chunk_elements` pieces so that the encode of
+    chunk k+1 and the decode of chunk k-1 overlap the wire time of chunk k.
+    With world == 1 the all-reduce degenerates to the single-GPU publication
+    (NNtrain.Core/Tensors/CudaBfp8GradientPublicationScope.cs:12-521): encode
+    with fused write-back, sum of squares and finite flag.
+    """
+
+    def __init__(self, group: GradientGroup, elements: int, block_size: int = 32, mode: int = PEER,
+                 chunk_elements: int | None = None, reduction_scale: float = 1.0,
+                 write_fp32: bool = True):
+        if block_size not in (32, 64, 128):
+            raise ValueError("block size must be 32, 64 or 128")
+        self.group, self.elements, self.block, self.mode = group, elements, block_size, mode
+        self.reduction_scale, self.write_fp32 = reduction_scale, write_fp32
+        world = group.world
+        align = 512 * world
+        if chunk_elements is None or chunk_elements >= elements:
+            chunk_elements = elements
+        else:
+            chunk_elements = max(align, chunk_elements // align * align)
+        self.chunk = chunk_elements
+        device = group.device
+        self.scale_count = (elements + block_size - 1) // block_size
+        with torch.cuda.device(device):
+            self.payload_buffer = PeerBuffer(group, elements)
+            self.scales_buffer = PeerBuffer(group, self.scale_count * 4)
+            self.payload = self.payload_buffer.tensor(torch.int8, elements)
+            self.scales = self.scales_buffer.tensor(torch.float32, self.scale_count)
+            self.squared_sum = torch.zeros(1, dtype=torch.float64, device=f"cuda:{device}")
+            self.finite_status = torch.zeros(1, dtype=torch.int32, device=f"cuda:{device}")
+            self.norm_and_coefficient = torch.zeros(2, dtype=torch.float32, device=f"cuda:{device}")
+            self.staging_payload = self.staging_scales = None
+            if mode == NCCL and world > 1:
+                first, end = shard_range(min(self.chunk, elements), world, 0)
+                shard = end - first
+                shard = (shard + 511) // 512 * 512
+                self.staging_payload = torch.empty(world * shard, dtype=torch.int8, device=f"cuda:{device}")
+                self.staging_scales = torch.empty(world * shard // block_size + world, dtype=torch.float32,
+                                                  device=f"cuda:{device}")
+            self.compute_stream = torch.cuda.Stream(device)
+            self.communication_stream = torch.cuda.Stream(device)
+            self.decode_stream = torch.cuda.Stream(device)
+            self.h2d_stream = torch.cuda.Stream(device)
+            self.d2h_stream = torch.cuda.Stream(device)
+            chunks = (elements + self.chunk - 1) // self.chunk
+            self.encoded = [torch.cuda.Event() for _ in range(chunks)]
+            self.reduced = [torch.cuda.Event() for _ in range(chunks)]
+            self.uploaded = [torch.cuda.Event() for _ in range(chunks)]
+        self.kernel_launches = 0
+
+    @property
+    def transport_bytes_per_step(self) -> int:
+        """Bytes this rank sends per step: 2 (N-1)/N (E + 4 ceil(E/block))
+        (the N = 2, block = 128 case is the reference's
+        2 (E + 4 ceil(E/128)), NNtrain.Core.Tests/CudaMix8GradientTransportTests.cs:267-270)."""
+        world = self.group.world
+        return 2 * (world - 1) * (self.elements + 4 * self.scale_count) // world
+
+    def enqueue(self, gradient: torch.Tensor, max_norm: float | None = None, host_gradient=None,
+                host_payload=None, host_scales=None) -> None:
+        """Enqueues one whole step for `gradient` (the fp32 arena) behind the
+        work already on the current stream.
+
+        With `host_gradient` (pinned fp32) each chunk is first copied host ->
+        device on its own stream, overlapping the previous chunk's kernels;
+        with `host_payload` / `host_scales` (pinned) the reduced payload is
+        copied back chunk by chunk as it becomes final and the (clipped) scale
+        sidecar at the end."""
+        group, device, lib = self.group, self.group.device, load()
+        world = group.world
+        current = torch.cuda.current_stream(device)
+        self.squared_sum.zero_()
+        self.finite_status.zero_()
+        ready = current.record_event()
+        for stream in (self.compute_stream, self.communication_stream, self.h2d_stream, self.d2h_stream):
+            stream.wait_event(ready)
+        launches = 2
+        spans = [(start, min(start + self.chunk, self.elements)) for start in range(0, self.elements, self.chunk)]
+        first_stream = self.communication_stream if world == 1 else self.compute_stream
+        pending = None      # chunk whose result becomes readable after the next collective
+        for index, (start, stop) in enumerate(spans):
+            src = gradient[start:stop]
+            payload = self.payload[start:stop]
+            scales = self.scales[start // self.block:(stop + self.block - 1) // self.block]
+            if host_gradient is not None:
+                with torch.cuda.stream(self.h2d_stream):
+                    src.copy_(host_gradient[start:stop], non_blocking=True)
+                    self.uploaded[index].record(self.h2d_stream)
+                first_stream.wait_event(self.uploaded[index])
+            if world == 1:
+                # single-GPU publication: encode + write-back + sum of squares + flag in one kernel
+                CudaBfp8Native.block_encode(device, src, payload, scales, self.block,
+                                            roundtrip=src if self.write_fp32 else None,
+                                            squared_sum=self.squared_sum, finite_status=self.finite_status,
+                                            stream=self.communication_stream)
+                launches += 1
+                self._result_final(index, (start, stop), gradient, host_payload, decode=False)
+                continue
+            CudaBfp8Native.block_encode(device, src, payload, scales, self.block,
+                                        finite_status=self.finite_status, stream=self.compute_stream)
+            self.encoded[index].record(self.compute_stream)
+            self.communication_stream.wait_event(self.encoded[index])
+            payload_table = _pointer_table([p + start for p in self.payload_buffer.pointers])
+            scales_table = _pointer_table([p + 4 * (start // self.block) for p in self.scales_buffer.pointers])
+            phase = (1 if index == 0 else 0) | (2 if index == len(spans) - 1 else 0)
+            check("gradient_allreduce_bfp8", lib.nntrain_gradient_allreduce_bfp8(
+                group.handle, payload_table, scales_table, stop - start, self.block, self.reduction_scale,
+                self.squared_sum.data_ptr(), self.finite_status.data_ptr(), self.mode, phase,
+                0 if self.staging_payload is None else self.staging_payload.data_ptr(),
+                0 if self.staging_scales is None else self.staging_scales.data_ptr(),
+                self.communication_stream.cuda_stream))
+            launches += 2 + (1 if phase & 1 else 0) + (2 if phase & 2 else 0)
+            # In peer mode a chunk's result is complete on every rank only
+            # after the NEXT collective on the group (the next chunk's leading
+            # barrier, or this chunk's own closing fence when it is the last).
+            if pending is not None:
+                launches += self._result_final(pending, spans[pending], gradient, host_payload, self.write_fp32)
+                pending = None
+            if self.mode == NCCL or phase & 2:
+                launches += self._result_final(index, (start, stop), gradient, host_payload, self.write_fp32)
+            else:
+                pending = index
+        with torch.cuda.stream(self.communication_stream):
+            if max_norm is not None:
+                GradientNorm.clip_coefficient(device, self.squared_sum, max_norm, self.norm_and_coefficient,
+                                              stream=self.communication_stream)
+                GradientNorm.clip_apply(device, GradientNorm.BFP8, self.scales,
+                                        coefficient=self.norm_and_coefficient, stream=self.communication_stream)
+                launches += 2
+            if host_scales is not None:
+                host_scales.copy_(self.scales, non_blocking=True)
+        self.communication_stream.wait_stream(self.decode_stream)
+        self.communication_stream.wait_stream(self.compute_stream)
+        self.communication_stream.wait_stream(self.d2h_stream)
+        current.wait_stream(self.communication_stream)
+        self.kernel_launches = launches
+
+    def _result_final(self, index: int, span, gradient, host_payload, decode: bool) -> int:
+        """Chunk `index` is final in stream order on the communication stream:
+        start its decode and its copy back to the host."""
+        start, stop = span
+        if not decode and host_payload is None:
+            return 0
+        self.reduced[index].record(self.communication_stream)
+        if host_payload is not None:
+            self.d2h_stream.wait_event(self.reduced[index])
+            with torch.cuda.stream(self.d2h_stream):
+                host_payload[start:stop].copy_(self.payload[start:stop], non_blocking=True)
+        if not decode:
+            return 0
+        self.decode_stream.wait_event(self.reduced[index])
+        CudaBfp8Native.block_decode(self.group.device, self.payload[start:stop],
+                                    self.scales[start // self.block:(stop + self.block - 1) // self.block],
+                                    gradient[start:stop], self.block, stream=self.decode_stream)
+        return 1
+
+    def complete(self, max_norm: float | None = None) -> StepResult:
+        """The step's only device-to-host read: sum of squares, finite flag and
+        (when clipping) norm + coefficient, 24 bytes."""
+        device = self.group.device
+        torch.cuda.current_stream(device).synchronize()
+        squared_sum = float(self.squared_sum.item())
+        finite = int(self.finite_status.item()) == 0
+        if max_norm is not None:
+            norm, coefficient = (float(v) for v in self.norm_and_coefficient.tolist())
+        else:
+            norm, coefficient = float(torch.tensor(squared_sum, dtype=torch.float64).sqrt().float()), 1.0
+        if not finite:
+            raise FloatingPointError("BFP8 gradient reduction saw a non-finite gradient")
+        return StepResult(norm, coefficient, squared_sum, finite)
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.group.device)
+        self.payload = self.scales = None
+        self.payload_buffer.close()
+        self.scales_buffer.close()
+
+
+def smoke_check(oracle) -> None:
+    """Two emulated ranks on one GPU: the owner kernel against the oracle."""
+    import numpy as np
+    n, block = 70001, 32
+    gradients = [oracle.generate_gradient(n, 0xB2000001, r) for r in range(2)]
+    payloads, scales = [], []
+    for g in gradients:
+        p = torch.empty(n, dtype=torch.int8, device="cuda")
+        s = torch.empty((n + block - 1) // block, dtype=torch.float32, device="cuda")
+        CudaBfp8Native.block_encode(0, torch.from_numpy(g).cuda(), p, s, block)
+        payloads.append(p)
+        scales.append(s)
+    for rank in range(2):
+        first, end = shard_range(n, 2, rank)
+        reduce_shards_bfp8(0, payloads, scales, payloads, scales, first, end, block, 0.5)
+    torch.cuda.synchronize()
+    expect_payload, expect_scales, _, _ = oracle.allreduce_bfp8(gradients, block, 0.5)
+    for p, s in zip(payloads, scales):
+        assert np.array_equal(p.cpu().numpy(), expect_payload), "reduced payload differs from the oracle"
+        assert np.array_equal(s.cpu().numpy().view(np.uint32), expect_scales.view(np.uint32)), "scales differ"

@@ -62,6 +62,8 @@ def parse_args():
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--cpu-sample-elements", type=int, default=64 << 20)
+    p.add_argument("--kernels", action="store_true",
+                   help="time every kernel of the path alone (one JSON line each) instead of the step")
     return p.parse_args()
 
 
@@ -234,8 +236,76 @@ def run_reference_arm(args, rank: int, world: int):
     print(json.dumps(line), flush=True)
 
 
+def time_kernels(args):
+    """Every kernel of the path timed alone with CUDA events on its stream:
+    algorithmic bytes / duration against the measured HBM peak."""
+    import torch
+    from nntrain_b200 import reducers
+    from nntrain_b200.native import CudaBfp8Native, CudaGradientBuckets, GradientNorm
+
+    torch.cuda.set_device(0)
+    E = min(args.elements, 256 << 20)
+    peak, kind = measured_peaks()
+    arena = torch.empty(E, dtype=torch.float32, device="cuda")
+    fill_gradient(arena, 0xB2000004, 0)
+    scratch = torch.empty_like(arena)
+    payload = torch.empty(E, dtype=torch.int8, device="cuda")
+    scales = torch.empty(E // 32, dtype=torch.float32, device="cuda")
+    scales128 = torch.empty(E // 128, dtype=torch.float32, device="cuda")
+    bf16 = torch.empty(E, dtype=torch.int16, device="cuda")
+    sq = torch.zeros(1, dtype=torch.float64, device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    CudaBfp8Native.block_encode(0, arena, payload, scales, 32)
+    replicas = [(payload.clone(), scales.clone()) for _ in range(7)]
+
+    def reduce_n(n):
+        ins = [(payload, scales)] + replicas[:n - 1]
+        first, end = 0, E // n // 512 * 512      # one rank's shard, as in the all-reduce
+        return (lambda: reducers.reduce_shards_bfp8(0, [p for p, _ in ins], [s for _, s in ins], [payload], [scales],
+                                                    first, end, 32, 1.0 / n, sq, flag),
+                (1.125 * n + 1.125) * (end - first))
+
+    cases = [
+        ("encode block32", lambda: CudaBfp8Native.block_encode(0, arena, payload, scales, 32), 5.125 * E),
+        ("encode block32 + finite flag", lambda: CudaBfp8Native.block_encode(0, arena, payload, scales, 32, finite_status=flag), 5.125 * E),
+        ("encode block32 publish (write-back + squares + flag)",
+         lambda: CudaBfp8Native.block_encode(0, arena, payload, scales, 32, roundtrip=scratch, squared_sum=sq, finite_status=flag), 9.125 * E),
+        ("encode block128", lambda: CudaBfp8Native.block_encode(0, arena, payload, scales128, 128), (5 + 4 / 128) * E),
+        ("pack bfp8 block128 (transport)", lambda: CudaGradientBuckets.pack_bfp8_block(0, arena, payload, scales128), (5 + 4 / 128) * E),
+        ("encode tensor-wide (3 passes)", lambda: CudaBfp8Native.block_encode(0, arena, payload, scales, 0), 9.0 * E),
+        ("decode block32", lambda: CudaBfp8Native.block_decode(0, payload, scales, scratch, 32), 5.125 * E),
+        ("pack bf16", lambda: CudaGradientBuckets.pack(0, arena, bf16, 0), 6.0 * E),
+        ("squared sum fp32", lambda: GradientNorm.squared_sum(0, GradientNorm.FP32, arena, sq), 4.0 * E),
+        ("squared sum bf16", lambda: GradientNorm.squared_sum(0, GradientNorm.BF16, bf16, sq), 2.0 * E),
+        ("squared sum bfp8", lambda: GradientNorm.squared_sum(0, GradientNorm.BFP8, payload, sq, scales, 32, flag), 1.125 * E),
+        ("clip bfp8 scales", lambda: GradientNorm.clip_apply(0, GradientNorm.BFP8, scales, multiplier=0.999), 0.25 * E),
+        ("clip fp32", lambda: GradientNorm.clip_apply(0, GradientNorm.FP32, scratch, multiplier=0.999), 8.0 * E),
+    ]
+    for n in (2, 4, 8):
+        fn, nbytes = reduce_n(n)
+        cases.append((f"owner reduce + re-encode, {n} local shards", fn, nbytes))
+    for name, fn, nbytes in cases:
+        for _ in range(3):
+            fn()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        runs = 10
+        begin.record()
+        for _ in range(runs):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        ms = begin.elapsed_time(end) / runs
+        achieved = nbytes / (ms * 1e-3) / 1e9
+        print(json.dumps({"kernel": name, "elements": E, "ms": round(ms, 4), "algorithmic_bytes": nbytes,
+                          "achieved_gbs": round(achieved, 1), "peak_gbs": peak, "peak_kind": kind,
+                          "frac": round(achieved / peak, 4)}), flush=True)
+
+
 def main():
     args = parse_args()
+    if args.kernels:
+        time_kernels(args)
+        return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

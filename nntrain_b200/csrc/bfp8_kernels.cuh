@@ -70,8 +70,9 @@ __device__ __forceinline__ void encode_block_scalar(
     const bool poison = (kFlags & kEncNanScale) && bad;
     if (poison) scale = __uint_as_float(0x7fffffffu);
     if (lane == 0) scales[scale_index] = scale;
+    const BlockScale divisor = block_scale(scale);
     for (long long i = start + lane; i < end; i += 32) {
-        const float t = poison ? kRoundMagic : biased_code_of(source[i], scale);
+        const float t = poison ? kRoundMagic : biased_code_of(source[i], divisor);
         payload[i] = code_byte(t);
         if (kFlags & (kEncWriteBack | kEncSquares)) {
             const float decoded = __fmul_rn(code_value(t), scale);
@@ -141,10 +142,11 @@ bfp8_encode_blocks_kernel(const float* __restrict__ source, float* writeback,
                 if (poison) {
                     t0 = t1 = t2 = t3 = kRoundMagic;
                 } else {
-                    t0 = biased_code_of(x.x, scale);
-                    t1 = biased_code_of(x.y, scale);
-                    t2 = biased_code_of(x.z, scale);
-                    t3 = biased_code_of(x.w, scale);
+                    const BlockScale divisor = block_scale(scale);
+                    t0 = biased_code_of(x.x, divisor);
+                    t1 = biased_code_of(x.y, divisor);
+                    t2 = biased_code_of(x.z, divisor);
+                    t3 = biased_code_of(x.w, divisor);
                 }
                 const long long at = base + j * 128 + lane * 4;
                 *reinterpret_cast<unsigned*>(payload + at) = pack_codes(t0, t1, t2, t3);
@@ -276,6 +278,7 @@ bfp8_segment_payload_kernel(const float* __restrict__ source, float* writeback,
         const long long end = start + block < length ? start + block : length;
         const long long span = end - start;
         const float scale = scale_from_maximum(maxima[segment]);
+        const BlockScale divisor = block_scale(scale);
         const float* base = source + start;
         signed char* out = payload + start;
         float* back = (kFlags & kEncWriteBack) ? writeback + start : nullptr;
@@ -286,8 +289,8 @@ bfp8_segment_payload_kernel(const float* __restrict__ source, float* writeback,
         const long long stride = static_cast<long long>(ctas_per_segment) * kThreads;
         for (long long i = static_cast<long long>(part) * kThreads + threadIdx.x; i < vectors; i += stride) {
             const float4 x = load_f4_stream(base + i * 4);
-            const float t0 = biased_code_of(x.x, scale), t1 = biased_code_of(x.y, scale),
-                        t2 = biased_code_of(x.z, scale), t3 = biased_code_of(x.w, scale);
+            const float t0 = biased_code_of(x.x, divisor), t1 = biased_code_of(x.y, divisor),
+                        t2 = biased_code_of(x.z, divisor), t3 = biased_code_of(x.w, divisor);
             *reinterpret_cast<unsigned*>(out + i * 4) = pack_codes(t0, t1, t2, t3);
             if (kFlags & (kEncWriteBack | kEncSquares)) {
                 float4 d;
@@ -305,7 +308,7 @@ bfp8_segment_payload_kernel(const float* __restrict__ source, float* writeback,
             }
         }
         for (long long i = vectors * 4 + static_cast<long long>(part) * kThreads + threadIdx.x; i < span; i += stride) {
-            const float t = biased_code_of(base[i], scale);
+            const float t = biased_code_of(base[i], divisor);
             out[i] = code_byte(t);
             if (kFlags & (kEncWriteBack | kEncSquares)) {
                 const float d = __fmul_rn(code_value(t), scale);

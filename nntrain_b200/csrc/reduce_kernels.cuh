@@ -115,9 +115,10 @@ bfp8_reduce_reencode_kernel(EncodedShards shards, long long first_value, long lo
             }
             m = group_max<kLanesPerBlock>(m);
             const float scale = scale_from_maximum(m);
+            const BlockScale divisor = block_scale(scale);
             float t[16];
             #pragma unroll
-            for (int i = 0; i < 16; ++i) t[i] = biased_code_of(acc[i], scale);
+            for (int i = 0; i < 16; ++i) t[i] = biased_code_of(acc[i], divisor);
             uint4 packed;
             packed.x = pack_codes(t[0], t[1], t[2], t[3]);
             packed.y = pack_codes(t[4], t[5], t[6], t[7]);
@@ -167,11 +168,12 @@ bfp8_reduce_reencode_kernel(EncodedShards shards, long long first_value, long lo
                 }
                 m = group_max<32>(m);
                 const float scale = scale_from_maximum(m);
+                const BlockScale divisor = block_scale(scale);
                 #pragma unroll
                 for (int e = 0; e < kPerLane; ++e) {
                     const long long i = start + lane + e * 32;
                     if (i < stop) {
-                        const float t = biased_code_of(value[e], scale);
+                        const float t = biased_code_of(value[e], divisor);
                         if (kSquares) {
                             const double d = static_cast<double>(__fmul_rn(code_value(t), scale));
                             squares += d * d;

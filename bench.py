@@ -64,6 +64,7 @@ def parse_args():
     p.add_argument("--cpu-sample-elements", type=int, default=64 << 20)
     p.add_argument("--kernels", action="store_true",
                    help="time every kernel of the path alone (one JSON line each) instead of the step")
+    p.add_argument("--only", default="", help="with --kernels: run only the cases whose name contains this")
     return p.parse_args()
 
 
@@ -285,6 +286,8 @@ def time_kernels(args):
         fn, nbytes = reduce_n(n)
         cases.append((f"owner reduce + re-encode, {n} local shards", fn, nbytes))
     for name, fn, nbytes in cases:
+        if args.only and args.only not in name:
+            continue
         for _ in range(3):
             fn()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -82,9 +82,44 @@ __device__ __forceinline__ void encode_block_scalar(
     }
 }
 
+// Lanes of the warp that share a block of kLanes * 4 values with this lane.
+template <int kLanes>
+__device__ __forceinline__ unsigned group_mask(int lane) {
+    if (kLanes == 32) return 0xffffffffu;
+    return ((1u << kLanes) - 1u) << (lane & ~(kLanes - 1));
+}
+
+template <int kLanes>
+__device__ __forceinline__ float group_max_masked(unsigned mask, float v) {
+    #pragma unroll
+    for (int offset = kLanes / 2; offset > 0; offset >>= 1)
+        v = fmaxf(v, __shfl_xor_sync(mask, v, offset));
+    return v;
+}
+
+// Maximum of an unsigned value over the block's lanes: one hardware
+// reduction when the block is the whole warp, a shuffle butterfly for 8- and
+// 16-lane blocks (a reduction with a partial mask costs one pass per distinct
+// mask in the warp).
+template <int kLanes>
+__device__ __forceinline__ unsigned group_max_bits(unsigned mask, unsigned v) {
+    if (kLanes == 32) return __reduce_max_sync(0xffffffffu, v);
+    #pragma unroll
+    for (int offset = kLanes / 2; offset > 0; offset >>= 1)
+        v = max(v, __shfl_xor_sync(mask, v, offset));
+    return v;
+}
+
 // Fast path.  Requires: source (and writeback) 16-byte aligned, payload
 // 4-byte aligned.  `length` may be ragged: the last partial warp tile falls
 // back to encode_block_scalar.
+//
+// Per row of 128 values each lane holds four.  The block maximum is one
+// integer max-reduction over the block's lanes on the bit patterns (|x| >= 0
+// orders like an unsigned integer).  A lane whose four values contain a NaN
+// or Inf (their sum is then not finite) contributes 0xffffffff instead, so a
+// reduced value >= 0x7f800000 marks a block that needs the exact, per-value
+// treatment of non-finite input; finite blocks never pay for it.
 template <int kBlock, int kFlags>
 __global__ void __launch_bounds__(kThreads)
 bfp8_encode_blocks_kernel(const float* __restrict__ source, float* writeback,
@@ -92,13 +127,13 @@ bfp8_encode_blocks_kernel(const float* __restrict__ source, float* writeback,
                           long long length, double* squared_sum, int* finite_status) {
     static_assert(kBlock == 32 || kBlock == 64 || kBlock == 128, "fast path block sizes");
     constexpr int kLanesPerBlock = kBlock / 4;
-    constexpr int kBlocksPerRow = 128 / kBlock;            // blocks per 128-value row
-    constexpr int kScalesPerTile = kBlocksPerRow * kEncodeUnroll;
 
     const int lane = threadIdx.x & 31;
     const long long warp = static_cast<long long>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
     const long long warps = static_cast<long long>(gridDim.x) * kWarpsPerCta;
     const long long tiles = (length + kWarpTile - 1) / kWarpTile;
+    const unsigned mask = group_mask<kLanesPerBlock>(lane);
+    const bool leader = (lane & (kLanesPerBlock - 1)) == 0;
 
     double squares = 0.0;
     int non_finite = 0;
@@ -106,57 +141,66 @@ bfp8_encode_blocks_kernel(const float* __restrict__ source, float* writeback,
     for (long long tile = warp; tile < tiles; tile += warps) {
         const long long base = tile * kWarpTile;
         if (base + kWarpTile <= length) {
+            const float* in = source + base + lane * 4;
+            signed char* out = payload + base + lane * 4;
+            float* back = (kFlags & kEncWriteBack) ? writeback + base + lane * 4 : nullptr;
+            float* scale_out = scales + base / kBlock + lane / kLanesPerBlock;
             float4 v[kEncodeUnroll];
             #pragma unroll
-            for (int j = 0; j < kEncodeUnroll; ++j)
-                v[j] = load_f4_stream(source + base + j * 128 + lane * 4);
+            for (int j = 0; j < kEncodeUnroll; ++j) v[j] = load_f4_stream(in + j * 128);
 
-            float tile_scale = 0.0f;   // scale this lane will store (lanes < kScalesPerTile)
             #pragma unroll
             for (int j = 0; j < kEncodeUnroll; ++j) {
                 const float4 x = v[j];
-                int bad = 0;
-                float m;
-                if (kFlags & (kEncFiniteFlag | kEncNanScale)) {
+                const float lane_max = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+                const float lane_sum = __fadd_rn(__fadd_rn(x.x, x.y), __fadd_rn(x.z, x.w));
+                const unsigned lane_bits = fabsf(lane_sum) < __int_as_float(0x7f800000)
+                                               ? __float_as_uint(lane_max) : 0xffffffffu;
+                const unsigned block_bits = group_max_bits<kLanesPerBlock>(mask, lane_bits);
+                float scale;
+                float t0, t1, t2, t3;
+                if (block_bits < 0x7f800000u) {
+                    scale = scale_from_maximum_fast(__uint_as_float(block_bits));
+                    biased_codes_of(x, block_scale(scale), t0, t1, t2, t3);
+                } else {
+                    // a NaN / Inf in the block, or four finite values whose sum
+                    // overflowed: the reference's per-value rules
                     const bool n0 = is_non_finite(x.x), n1 = is_non_finite(x.y),
                                n2 = is_non_finite(x.z), n3 = is_non_finite(x.w);
-                    bad = n0 | n1 | n2 | n3;
+                    const int bad = n0 | n1 | n2 | n3;
+                    float m;
                     if (kFlags & kEncNanScale) {
                         m = fmaxf(fmaxf(n0 ? 0.0f : fabsf(x.x), n1 ? 0.0f : fabsf(x.y)),
                                   fmaxf(n2 ? 0.0f : fabsf(x.z), n3 ? 0.0f : fabsf(x.w)));
                     } else {
-                        m = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+                        m = fmaxf(fmaxf(fmaxf(0.0f, fabsf(x.x)), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
                     }
                     if (kFlags & kEncFiniteFlag) non_finite |= bad;
-                } else {
-                    m = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+                    m = group_max_masked<kLanesPerBlock>(mask, m);
+                    scale = scale_from_maximum(m);
+                    bool poison = false;
+                    if (kFlags & kEncNanScale) {
+                        poison = __reduce_or_sync(mask, static_cast<unsigned>(bad)) != 0;
+                        if (poison) scale = __uint_as_float(0x7fffffffu);
+                    }
+                    if (poison) {
+                        t0 = t1 = t2 = t3 = kRoundMagic;
+                    } else {
+                        t0 = biased_code_of(x.x, scale);
+                        t1 = biased_code_of(x.y, scale);
+                        t2 = biased_code_of(x.z, scale);
+                        t3 = biased_code_of(x.w, scale);
+                    }
                 }
-                m = group_max<kLanesPerBlock>(m);
-                float scale = scale_from_maximum(m);
-                bool poison = false;
-                if (kFlags & kEncNanScale) {
-                    poison = group_or<kLanesPerBlock>(bad) != 0;
-                    if (poison) scale = __uint_as_float(0x7fffffffu);
-                }
-                float t0, t1, t2, t3;
-                if (poison) {
-                    t0 = t1 = t2 = t3 = kRoundMagic;
-                } else {
-                    const BlockScale divisor = block_scale(scale);
-                    t0 = biased_code_of(x.x, divisor);
-                    t1 = biased_code_of(x.y, divisor);
-                    t2 = biased_code_of(x.z, divisor);
-                    t3 = biased_code_of(x.w, divisor);
-                }
-                const long long at = base + j * 128 + lane * 4;
-                *reinterpret_cast<unsigned*>(payload + at) = pack_codes(t0, t1, t2, t3);
+                *reinterpret_cast<unsigned*>(out + j * 128) = pack_codes(t0, t1, t2, t3);
+                if (leader) scale_out[j * (128 / kBlock)] = scale;
                 if (kFlags & (kEncWriteBack | kEncSquares)) {
                     float4 d;
                     d.x = __fmul_rn(code_value(t0), scale);
                     d.y = __fmul_rn(code_value(t1), scale);
                     d.z = __fmul_rn(code_value(t2), scale);
                     d.w = __fmul_rn(code_value(t3), scale);
-                    if (kFlags & kEncWriteBack) store_f4(writeback + at, d);
+                    if (kFlags & kEncWriteBack) store_f4(back + j * 128, d);
                     if (kFlags & kEncSquares) {
                         squares += static_cast<double>(d.x) * static_cast<double>(d.x);
                         squares += static_cast<double>(d.y) * static_cast<double>(d.y);
@@ -164,13 +208,7 @@ bfp8_encode_blocks_kernel(const float* __restrict__ source, float* writeback,
                         squares += static_cast<double>(d.w) * static_cast<double>(d.w);
                     }
                 }
-                // Route this row's scales to the lanes that will store them:
-                // lane L stores the scale of row L / kBlocksPerRow, block
-                // L % kBlocksPerRow of that row.
-                const float routed = __shfl_sync(0xffffffffu, scale, (lane % kBlocksPerRow) * kLanesPerBlock);
-                if (lane / kBlocksPerRow == j) tile_scale = routed;
             }
-            if (lane < kScalesPerTile) scales[base / kBlock + lane] = tile_scale;
         } else {
             for (long long start = base; start < length; start += kBlock) {
                 const long long end = start + kBlock < length ? start + kBlock : length;

@@ -81,6 +81,23 @@ __device__ __forceinline__ float scale_from_maximum(float maximum) {
     return maximum == 0.0f ? 1.0f : __fdiv_rn(maximum, 127.0f);
 }
 
+// The same value in three FP32 instructions when the maximum lies in
+// [2^-90, 2^100]: q0 = m * r, e = fma(-127, q0, m), q = fma(e, r, q0) with
+// r = fl(1/127).  For the divisor 127 this sequence returns the correctly
+// rounded quotient for every binary32 significand (checked exhaustively over
+// all 2^23 of them; scaling by a power of two carries the result to every
+// exponent at which nothing underflows, hence the range test).  Outside the
+// range, and for zero, the IEEE division above is used.
+__device__ __forceinline__ float scale_from_maximum_fast(float maximum) {
+    if (maximum >= 8.0779356694631609e-28f && maximum <= 1.2676506002282294e30f) {
+        constexpr float kReciprocal = 1.0f / 127.0f;
+        const float q0 = __fmul_rn(maximum, kReciprocal);
+        const float e = __fmaf_rn(-127.0f, q0, maximum);
+        return __fmaf_rn(e, kReciprocal, q0);
+    }
+    return scale_from_maximum(maximum);
+}
+
 // Round-half-even of a quotient to an integer in [-127,127], NaN -> 0
 // (Bfp8Quantization.cs:220-227), kept in "biased" form: the returned float is
 // code + 1.5 * 2^23, whose low mantissa byte is the two's-complement int8
@@ -132,6 +149,31 @@ __device__ __forceinline__ float biased_code_of(float value, const BlockScale& b
     const float distance = fabsf(__fadd_rn(raw, -__fadd_rn(t, -kRoundMagic)));
     if (b.fast && distance < 0.4999f) return t;
     return biased_code_of(value, b.scale);
+}
+
+// Four values of one block at once: one decision for the (rare) exact path.
+__device__ __forceinline__ void biased_codes_of(const float4& x, const BlockScale& b,
+                                                float& t0, float& t1, float& t2, float& t3) {
+    const float r0 = __fmul_rn(x.x, b.inverse), r1 = __fmul_rn(x.y, b.inverse),
+                r2 = __fmul_rn(x.z, b.inverse), r3 = __fmul_rn(x.w, b.inverse);
+    t0 = __fadd_rn(r0, kRoundMagic);
+    t1 = __fadd_rn(r1, kRoundMagic);
+    t2 = __fadd_rn(r2, kRoundMagic);
+    t3 = __fadd_rn(r3, kRoundMagic);
+    // The scale is the block maximum / 127, so |r| <= 127.00003 and no clamp
+    // is needed here; a NaN or Inf value makes its distance NaN, fails the
+    // comparison and takes the exact path.
+    const float d0 = fabsf(__fadd_rn(r0, -__fadd_rn(t0, -kRoundMagic)));
+    const float d1 = fabsf(__fadd_rn(r1, -__fadd_rn(t1, -kRoundMagic)));
+    const float d2 = fabsf(__fadd_rn(r2, -__fadd_rn(t2, -kRoundMagic)));
+    const float d3 = fabsf(__fadd_rn(r3, -__fadd_rn(t3, -kRoundMagic)));
+    const bool ok = b.fast && (d0 < 0.4999f) && (d1 < 0.4999f) && (d2 < 0.4999f) && (d3 < 0.4999f);
+    if (!ok) {
+        t0 = biased_code_of(x.x, b.scale);
+        t1 = biased_code_of(x.y, b.scale);
+        t2 = biased_code_of(x.z, b.scale);
+        t3 = biased_code_of(x.w, b.scale);
+    }
 }
 
 // The code as an integer-valued float (for decode = code * scale).

@@ -114,11 +114,15 @@ bfp8_reduce_reencode_kernel(EncodedShards shards, long long first_value, long lo
                 m = fmaxf(m, fabsf(acc[i]));
             }
             m = group_max<kLanesPerBlock>(m);
-            const float scale = scale_from_maximum(m);
+            // a NaN sum is dropped by fmaxf and an Inf one gives scale = Inf;
+            // both are flagged above and take the exact per-value path below
+            const float scale = scale_from_maximum_fast(m);
             const BlockScale divisor = block_scale(scale);
             float t[16];
             #pragma unroll
-            for (int i = 0; i < 16; ++i) t[i] = biased_code_of(acc[i], divisor);
+            for (int i = 0; i < 16; i += 4)
+                biased_codes_of(make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]), divisor,
+                                t[i], t[i + 1], t[i + 2], t[i + 3]);
             uint4 packed;
             packed.x = pack_codes(t[0], t[1], t[2], t[3]);
             packed.y = pack_codes(t[4], t[5], t[6], t[7]);

@@ -193,3 +193,24 @@ def test_encode_decode_encode_is_idempotent_at_full_bucket_size(cuda):
     # a block's largest code is +-127 unless the block is all zero
     top = payload.view(-1, 32).to(torch.int16).abs().amax(dim=1)
     assert bool(((top == 127) | (scales == 1.0)).all())
+
+
+@pytest.mark.parametrize("exponent_bits", (0x3F800000, 0x12800000, 0x71000000, 0x00800000, 0x7E800000))
+def test_scale_is_the_ieee_quotient_for_every_significand(cuda, exponent_bits):
+    """One block per binary32 significand (2^23 blocks), the block's only
+    non-zero value being that significand at the given exponent: the stored
+    scale must be the correctly rounded max / 127 for all of them, in the fast
+    range and outside it."""
+    count = 1 << 23
+    bits = torch.arange(count, dtype=torch.int32, device="cuda") + exponent_bits
+    maxima = bits.view(torch.float32)
+    source = torch.zeros(count * 32, dtype=torch.float32, device="cuda")
+    source[7::32] = -maxima
+    payload = torch.empty(count * 32, dtype=torch.int8, device="cuda")
+    scales = torch.empty(count, dtype=torch.float32, device="cuda")
+    CudaBfp8Native.block_encode(0, source, payload, scales, 32)
+    torch.cuda.synchronize()
+    expect = host(maxima) / np.float32(127.0)
+    assert_bits_equal(host(scales), expect, "scales")
+    codes = host(payload[7::32])
+    assert (codes == -127).all()

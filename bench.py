@@ -59,6 +59,8 @@ def parse_args():
     p.add_argument("--elements", type=int, default=QWEN2_1P5B_ELEMENTS)
     p.add_argument("--mode", choices=("peer", "nccl"), default="peer")
     p.add_argument("--chunk-elements", type=int, default=0, help="0 = pick by world size")
+    p.add_argument("--codec-iterations", type=int, default=-1, help="-1 = library default for the run")
+    p.add_argument("--collective-ctas", type=int, default=-1, help="-1 = library default for the run")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--cpu-sample-elements", type=int, default=64 << 20)
@@ -334,8 +336,11 @@ def main():
     mode = reducers.PEER if args.mode == "peer" else reducers.NCCL
     chunk = args.chunk_elements or (0 if world == 1 else 128 << 20)
     group = reducers.GradientGroup(world, rank, local_rank)
+    shape = dict(codec_iterations_per_cta=None if args.codec_iterations < 0 else args.codec_iterations,
+                 collective_ctas=None if args.collective_ctas < 0 else args.collective_ctas)
     step = reducers.Bfp8ArenaAllReduce(group, E, BLOCK, mode, chunk_elements=chunk or None,
-                                       reduction_scale=1.0 / world, write_fp32=True)
+                                       reduction_scale=1.0 / world, write_fp32=True, **shape)
+    device_chunk, device_shape = step.chunk, (step.codec_iterations_per_cta, step.collective_ctas)
     arena = torch.empty(E, dtype=torch.float32, device=device)
     fill_gradient(arena, 0xB2000004, rank)
     torch.cuda.synchronize()
@@ -411,7 +416,7 @@ def main():
         if e2e_step is None:
             step.close()
             e2e_step = reducers.Bfp8ArenaAllReduce(group, E, BLOCK, mode, chunk_elements=e2e_chunk,
-                                                   reduction_scale=1.0 / world, write_fp32=True)
+                                                   reduction_scale=1.0 / world, write_fp32=True, **shape)
         e2e_steps = max(1, min(args.steps, 5))
         for _ in range(min(args.warmup, 2)):
             e2e_step.enqueue(arena, MAX_NORM, host_gradient, host_payload, host_scales)
@@ -459,7 +464,8 @@ def main():
             "config": {"workload": "qwen2-1.5b gradient arena, BFP8 block-32 all-reduce + decode + clip-norm",
                        "elements_per_rank": E, "block": BLOCK, "max_norm": MAX_NORM,
                        "transport": args.mode if world > 1 else "none (single-GPU publication)",
-                       "chunk_elements": step.chunk, "reduction": "mean (reduction_scale 1/N)",
+                       "chunk_elements": device_chunk, "codec_iterations_per_cta": device_shape[0],
+                       "collective_ctas": device_shape[1], "reduction": "mean (reduction_scale 1/N)",
                        "l2": "inputs (6.2 GB per rank) exceed the 126 MB L2; no flush needed",
                        "fp32_result": "arena overwritten with decode(encode(sum)) every step"},
             "algbw_gbs": algbw, "busbw_gbs": busbw,

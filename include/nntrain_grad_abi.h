@@ -64,6 +64,14 @@ int nntrain_cuda_set_device(int device);
  * NNtrain.Cuda/native/tensor_kernels.cu:26,2888-2891 */
 int nntrain_cuda_use_external_stream(void* stream);
 
+/* ABI minor 36; no counterpart in the reference (its kernels use fixed
+ * grids).  Launch shapes for overlapping the collective with the codec kernels
+ * of neighbouring chunks.  codec_iterations_per_cta: 0 = persistent grids (best
+ * for a kernel running alone), n > 0 = short-lived CTAs of n iterations each.
+ * collective_ctas: 0 = the all-reduce kernels fill the machine, n > 0 = at most
+ * n CTAs.  Process-wide. */
+int nntrain_gradient_configure(int codec_iterations_per_cta, int collective_ctas);
+
 /* ---- BFP8 block codec ---------------------------------------------------
  * payload: signed int8 per value; scales: one fp32 per block,
  * scale = max|x| == 0 ? 1 : max|x| / 127; code = clamp(rne(x / scale), +-127).

@@ -6,6 +6,7 @@
 #include "common.cuh"
 
 #include <array>
+#include <atomic>
 #include <mutex>
 
 namespace ngb {
@@ -22,6 +23,9 @@ thread_local cudaStream_t t_implicit_stream = nullptr;
 
 constexpr int kMaxDevices = 64;
 int g_sm_counts[kMaxDevices] = {};
+
+std::atomic<int> g_codec_iterations_per_cta{0};
+std::atomic<int> g_collective_ctas{0};
 
 }  // namespace
 
@@ -44,6 +48,16 @@ int select_device(int device) {
 }
 
 cudaStream_t& implicit_stream() { return t_implicit_stream; }
+
+LaunchPolicy launch_policy() {
+    return LaunchPolicy{g_codec_iterations_per_cta.load(std::memory_order_relaxed),
+                        g_collective_ctas.load(std::memory_order_relaxed)};
+}
+
+void set_launch_policy(int codec_iterations_per_cta, int collective_ctas) {
+    g_codec_iterations_per_cta.store(codec_iterations_per_cta, std::memory_order_relaxed);
+    g_collective_ctas.store(collective_ctas, std::memory_order_relaxed);
+}
 
 int sm_count() {
     int device = 0;
@@ -114,6 +128,17 @@ NNTRAIN_EXPORT int nntrain_capability_bitmap(int device, unsigned long long* bit
 
 NNTRAIN_EXPORT int nntrain_cuda_set_device(int device) {
     return complete(kOpSetDevice, device, select_device(device));
+}
+
+// Launch shapes for overlapping the collective with the codec kernels of
+// neighbouring chunks (ABI minor 36; the reference has no counterpart: its
+// kernels use fixed grids).  codec_iterations_per_cta: 0 = persistent grids,
+// n > 0 = short-lived CTAs of n iterations each.  collective_ctas: 0 = fill the
+// machine, n > 0 = at most n CTAs for the all-reduce kernels.
+NNTRAIN_EXPORT int nntrain_gradient_configure(int codec_iterations_per_cta, int collective_ctas) {
+    if (codec_iterations_per_cta < 0 || collective_ctas < 0) return static_cast<int>(cudaErrorInvalidValue);
+    set_launch_policy(codec_iterations_per_cta, collective_ctas);
+    return static_cast<int>(cudaSuccess);
 }
 
 NNTRAIN_EXPORT int nntrain_cuda_use_external_stream(void* stream) {

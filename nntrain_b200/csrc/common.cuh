@@ -20,6 +20,8 @@
 
 namespace ngb {
 
+constexpr int kCtasPerSmDefault = 8;
+
 // ---- ABI / status ---------------------------------------------------------
 // Same numbering as the reference's native layer
 // (NNtrain.Cuda/native/cuda_runtime_bridge.cu:18-21,23-72).
@@ -60,11 +62,41 @@ cudaStream_t& implicit_stream();
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
-// Persistent-style grid: enough CTAs to fill every SM `per_sm` times, never
-// more than the work needs.
+// Launch shape policy (process-wide, set by nntrain_gradient_configure):
+//   codec_iterations_per_cta  0: persistent grids (enough CTAs to fill every
+//       SM, each looping over the whole input) - best for a kernel running
+//       alone.  n > 0: every CTA does n loop iterations and retires, so that a
+//       kernel on another stream (the collective) finds free SM slots while a
+//       codec kernel runs.
+//   collective_ctas  0: the all-reduce kernels also fill the machine.  n > 0:
+//       they use at most n CTAs and leave the rest of the SMs' capacity to the
+//       codec kernels of the neighbouring chunks.
+struct LaunchPolicy {
+    int codec_iterations_per_cta;
+    int collective_ctas;
+};
+LaunchPolicy launch_policy();
+void set_launch_policy(int codec_iterations_per_cta, int collective_ctas);
+
+// Grid for `work_items` CTA-sized loop iterations: persistent (fill every SM
+// `per_sm` times, never more than the work needs) or, under the policy above,
+// one CTA per few iterations.
 inline int grid_for(long long work_items, int per_sm) {
-    long long cap = static_cast<long long>(sm_count()) * per_sm;
     if (work_items < 1) work_items = 1;
+    const int iterations = launch_policy().codec_iterations_per_cta;
+    if (iterations > 0) {
+        const long long ctas = (work_items + iterations - 1) / iterations;
+        return static_cast<int>(ctas < 2147483647ll ? ctas : 2147483647ll);
+    }
+    const long long cap = static_cast<long long>(sm_count()) * per_sm;
+    return static_cast<int>(work_items < cap ? work_items : cap);
+}
+
+// Grid for the all-reduce kernels.
+inline int collective_grid_for(long long work_items) {
+    if (work_items < 1) work_items = 1;
+    long long cap = launch_policy().collective_ctas;
+    if (cap <= 0) cap = static_cast<long long>(sm_count()) * kCtasPerSmDefault;
     return static_cast<int>(work_items < cap ? work_items : cap);
 }
 

@@ -13,7 +13,7 @@ cudaError_t run_reencode(const EncodedShards& shards, long long first_value, lon
                          float reduction_scale, double* squared_sum, int* finite_status,
                          bool vector_ok, cudaStream_t stream) {
     const long long tiles = (end_value - first_value + 511) / 512;
-    const int grid = grid_for((tiles + kWarpsPerCta - 1) / kWarpsPerCta, kCtasPerSm);
+    const int grid = collective_grid_for((tiles + kWarpsPerCta - 1) / kWarpsPerCta);
     if (squared_sum != nullptr) {
         bfp8_reduce_reencode_kernel<kBlock, kRanks, true><<<grid, kThreads, 0, stream>>>(
             shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok);
@@ -121,7 +121,7 @@ cudaError_t launch_bf16_reduce(const Bf16Inputs& io, float* reduced, long long f
         vector_ok = vector_ok && aligned_to(io.out_bf16[d], 16);
     }
     const long long groups = (end_value - first_value + 7) / 8;
-    const int grid = grid_for((groups + kThreads - 1) / kThreads, kCtasPerSm);
+    const int grid = collective_grid_for((groups + kThreads - 1) / kThreads);
     if (!squared_sum)
         bf16_reduce_kernel<false, false><<<grid, kThreads, 0, stream>>>(io, reduced, first_value, end_value, reduction_scale, nullptr, vector_ok);
     else if (square_of_bf16)

@@ -197,7 +197,8 @@ class Bfp8ArenaAllReduce:
 
     def __init__(self, group: GradientGroup, elements: int, block_size: int = 32, mode: int = PEER,
                  chunk_elements: int | None = None, reduction_scale: float = 1.0,
-                 write_fp32: bool = True):
+                 write_fp32: bool = True, codec_iterations_per_cta: int | None = None,
+                 collective_ctas: int | None = None):
         if block_size not in (32, 64, 128):
             raise ValueError("block size must be 32, 64 or 128")
         self.group, self.elements, self.block, self.mode = group, elements, block_size, mode
@@ -227,8 +228,18 @@ class Bfp8ArenaAllReduce:
                 self.staging_payload = torch.empty(world * shard, dtype=torch.int8, device=f"cuda:{device}")
                 self.staging_scales = torch.empty(world * shard // block_size + world, dtype=torch.float32,
                                                   device=f"cuda:{device}")
+            # Overlap shape: with more than one chunk in flight the codec kernels
+            # use short-lived CTAs and the all-reduce kernel a capped grid on a
+            # high-priority stream, so the three stages share the SMs.
+            overlapped = world > 1 and self.chunk < elements
+            if codec_iterations_per_cta is None:
+                codec_iterations_per_cta = 4 if overlapped else 0
+            if collective_ctas is None:
+                collective_ctas = 2 * torch.cuda.get_device_properties(device).multi_processor_count if overlapped else 0
+            self.codec_iterations_per_cta, self.collective_ctas = codec_iterations_per_cta, collective_ctas
+            check("gradient_configure", load().nntrain_gradient_configure(codec_iterations_per_cta, collective_ctas))
             self.compute_stream = torch.cuda.Stream(device)
-            self.communication_stream = torch.cuda.Stream(device)
+            self.communication_stream = torch.cuda.Stream(device, priority=-1)
             self.decode_stream = torch.cuda.Stream(device)
             self.h2d_stream = torch.cuda.Stream(device)
             self.d2h_stream = torch.cuda.Stream(device)

@@ -57,8 +57,9 @@ def parse_args():
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", choices=("b200", "reference"), default="b200")
     p.add_argument("--elements", type=int, default=QWEN2_1P5B_ELEMENTS)
-    p.add_argument("--mode", choices=("peer", "nccl"), default="peer")
+    p.add_argument("--mode", choices=("peer", "nccl", "copy"), default="peer")
     p.add_argument("--chunk-elements", type=int, default=0, help="0 = pick by world size")
+    p.add_argument("--chunk-plan", default="", help="comma-separated chunk lengths in Mi values (overrides --chunk-elements)")
     p.add_argument("--codec-iterations", type=int, default=-1, help="-1 = library default for the run")
     p.add_argument("--collective-ctas", type=int, default=-1, help="-1 = library default for the run")
     p.add_argument("--no-e2e", action="store_true")
@@ -66,6 +67,8 @@ def parse_args():
     p.add_argument("--cpu-sample-elements", type=int, default=64 << 20)
     p.add_argument("--kernels", action="store_true",
                    help="time every kernel of the path alone (one JSON line each) instead of the step")
+    p.add_argument("--phases", action="store_true",
+                   help="time encode, all-reduce and decode of the step separately (one JSON line)")
     p.add_argument("--only", default="", help="with --kernels: run only the cases whose name contains this")
     return p.parse_args()
 
@@ -306,6 +309,61 @@ def time_kernels(args):
                           "frac": round(achieved / peak, 4)}), flush=True)
 
 
+def time_phases(args, step, arena, world, rank, local_rank, barrier):
+    """Encode, all-reduce and decode of one whole-arena step, each timed alone
+    (CUDA events, max over ranks): shows what the overlapped step is made of."""
+    import ctypes
+
+    import torch
+    import torch.distributed as dist
+    from nntrain_b200 import reducers
+    from nntrain_b200.library import check, load
+    from nntrain_b200.native import CudaBfp8Native
+
+    lib, E = load(), step.elements
+    stream = torch.cuda.current_stream()
+
+    def encode():
+        CudaBfp8Native.block_encode(local_rank, arena, step.payload, step.scales, BLOCK,
+                                    finite_status=step.finite_status)
+
+    def allreduce():
+        table_p = (ctypes.c_void_p * world)(*step.payload_buffer.pointers)
+        table_s = (ctypes.c_void_p * world)(*step.scales_buffer.pointers)
+        check("allreduce", lib.nntrain_gradient_allreduce_bfp8(
+            step.group.handle, table_p, table_s, E, BLOCK, 1.0 / world, step.squared_sum.data_ptr(),
+            step.finite_status.data_ptr(), step.mode, 3,
+            0 if step.staging_payload is None else step.staging_payload.data_ptr(),
+            0 if step.staging_scales is None else step.staging_scales.data_ptr(), stream.cuda_stream))
+
+    def decode():
+        CudaBfp8Native.block_decode(local_rank, step.payload, step.scales, arena, BLOCK)
+
+    out = {}
+    for name, fn in (("encode", encode), ("allreduce", allreduce), ("decode", decode)):
+        for _ in range(2):
+            fn()
+        barrier()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(args.steps):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        barrier()
+        t = torch.tensor([begin.elapsed_time(end) / args.steps], dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[name + "_ms"] = round(float(t.item()), 4)
+    wire = 2 * (world - 1) / world * (E + 4 * step.scale_count)
+    out["allreduce_busbw_gbs"] = round(wire / (out["allreduce_ms"] * 1e-3) / 1e9, 1) if world > 1 else 0.0
+    if rank == 0:
+        print(json.dumps({"phases": out, "n_gpus": world, "elements_per_rank": E, "transport": args.mode,
+                          "collective_ctas": step.collective_ctas,
+                          "codec_iterations_per_cta": step.codec_iterations_per_cta}), flush=True)
+
+
 def main():
     args = parse_args()
     if args.kernels:
@@ -333,13 +391,15 @@ def main():
         dist.init_process_group("cpu:gloo,cuda:nccl", device_id=device)
 
     E = args.elements
-    mode = reducers.PEER if args.mode == "peer" else reducers.NCCL
+    mode = {"peer": reducers.PEER, "nccl": reducers.NCCL, "copy": reducers.COPY_ENGINE}[args.mode]
     chunk = args.chunk_elements or (0 if world == 1 else 128 << 20)
     group = reducers.GradientGroup(world, rank, local_rank)
     shape = dict(codec_iterations_per_cta=None if args.codec_iterations < 0 else args.codec_iterations,
-                 collective_ctas=None if args.collective_ctas < 0 else args.collective_ctas)
+                 collective_ctas=None if args.collective_ctas < 0 else args.collective_ctas,
+                 chunk_plan=[int(float(c) * (1 << 20)) for c in args.chunk_plan.split(",")] if args.chunk_plan else None)
     step = reducers.Bfp8ArenaAllReduce(group, E, BLOCK, mode, chunk_elements=chunk or None,
                                        reduction_scale=1.0 / world, write_fp32=True, **shape)
+    device_chunks = [b - a for a, b in step.spans]
     device_chunk, device_shape = step.chunk, (step.codec_iterations_per_cta, step.collective_ctas)
     arena = torch.empty(E, dtype=torch.float32, device=device)
     fill_gradient(arena, 0xB2000004, rank)
@@ -348,6 +408,14 @@ def main():
     def barrier():
         if world > 1:
             dist.barrier()
+
+    if args.phases:
+        time_phases(args, step, arena, world, rank, local_rank, barrier)
+        step.close()
+        group.close()
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # -- device-resident timing -----------------------------------------------------
     for _ in range(args.warmup):
@@ -416,7 +484,8 @@ def main():
         if e2e_step is None:
             step.close()
             e2e_step = reducers.Bfp8ArenaAllReduce(group, E, BLOCK, mode, chunk_elements=e2e_chunk,
-                                                   reduction_scale=1.0 / world, write_fp32=True, **shape)
+                                                   reduction_scale=1.0 / world, write_fp32=True,
+                                                   **{**shape, "chunk_plan": None})
         e2e_steps = max(1, min(args.steps, 5))
         for _ in range(min(args.warmup, 2)):
             e2e_step.enqueue(arena, MAX_NORM, host_gradient, host_payload, host_scales)
@@ -464,7 +533,7 @@ def main():
             "config": {"workload": "qwen2-1.5b gradient arena, BFP8 block-32 all-reduce + decode + clip-norm",
                        "elements_per_rank": E, "block": BLOCK, "max_norm": MAX_NORM,
                        "transport": args.mode if world > 1 else "none (single-GPU publication)",
-                       "chunk_elements": device_chunk, "codec_iterations_per_cta": device_shape[0],
+                       "chunk_elements": device_chunk, "chunks": device_chunks, "codec_iterations_per_cta": device_shape[0],
                        "collective_ctas": device_shape[1], "reduction": "mean (reduction_scale 1/N)",
                        "l2": "inputs (6.2 GB per rank) exceed the 126 MB L2; no flush needed",
                        "fp32_result": "arena overwritten with decode(encode(sum)) every step"},

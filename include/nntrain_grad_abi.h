@@ -277,13 +277,22 @@ int nntrain_gradient_reduce_shards_bf16(
     float reduction_scale, double* squared_sum, int square_of_bf16, nntrain_stream_t stream);
 /* In-place BFP8 all-reduce of an encoded arena (or one chunk of it).
  * mode 0: peer memory, one fused reduce-scatter + accumulate + re-encode +
- * all-gather kernel; mode 1: NCCL send/recv through staging (world shards).
+ * all-gather kernel; mode 1: NCCL send/recv through staging (world shards);
+ * mode 2: copy engines pull the peers' shards into the same staging and push
+ * the reduced shard back, the owner kernel runs on local memory.
  * phase: bit 0 = first chunk of a step, bit 1 = last chunk (fence, sum of
- * squares and finite flag summed over ranks and published); 3 = whole arena. */
+ * squares and finite flag summed over ranks and published); 3 = whole arena.
+ * previous_final (optional event): recorded behind the call's leading barrier,
+ * the point at which every earlier chunk of the step is complete here. */
 int nntrain_gradient_allreduce_bfp8(
     void* group, signed char* const* payload_by_rank, float* const* scales_by_rank, long long length,
     int block_size, float reduction_scale, double* squared_sum, int* finite_status, int mode,
-    int phase, signed char* staging_payload, float* staging_scales, nntrain_stream_t stream);
+    int phase, signed char* staging_payload, float* staging_scales, nntrain_event_t previous_final,
+    nntrain_stream_t stream);
+/* Makes `stream` wait for `event` (cudaStreamWaitEvent on opaque handles; the
+ * reference does this inside its exchange entry points,
+ * NNtrain.Cuda/native/gradient_collectives.cu:284-291). */
+int nntrain_gradient_stream_wait_event(nntrain_stream_t stream, nntrain_event_t event);
 /* In-place bf16 arena all-reduce (fp32 accumulate, bf16 result); mode and
  * phase as above. */
 int nntrain_gradient_allreduce_bf16(

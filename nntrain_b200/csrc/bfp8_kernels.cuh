@@ -85,8 +85,11 @@ __device__ __forceinline__ void encode_block_scalar(
 // Lanes of the warp that share a block of kLanes * 4 values with this lane.
 template <int kLanes>
 __device__ __forceinline__ unsigned group_mask(int lane) {
-    if (kLanes == 32) return 0xffffffffu;
-    return ((1u << kLanes) - 1u) << (lane & ~(kLanes - 1));
+    if constexpr (kLanes == 32) {
+        return 0xffffffffu;
+    } else {
+        return ((1u << kLanes) - 1u) << (lane & ~(kLanes - 1));
+    }
 }
 
 template <int kLanes>
@@ -103,11 +106,14 @@ __device__ __forceinline__ float group_max_masked(unsigned mask, float v) {
 // mask in the warp).
 template <int kLanes>
 __device__ __forceinline__ unsigned group_max_bits(unsigned mask, unsigned v) {
-    if (kLanes == 32) return __reduce_max_sync(0xffffffffu, v);
-    #pragma unroll
-    for (int offset = kLanes / 2; offset > 0; offset >>= 1)
-        v = max(v, __shfl_xor_sync(mask, v, offset));
-    return v;
+    if constexpr (kLanes == 32) {
+        return __reduce_max_sync(0xffffffffu, v);
+    } else {
+        #pragma unroll
+        for (int offset = kLanes / 2; offset > 0; offset >>= 1)
+            v = max(v, __shfl_xor_sync(mask, v, offset));
+        return v;
+    }
 }
 
 // Fast path.  Requires: source (and writeback) 16-byte aligned, payload

@@ -23,6 +23,11 @@
 //   nccl (mode 1): grouped ncclSend/ncclRecv of encoded shards into local
 //     staging, the same owner kernel on local memory, grouped send/recv of the
 //     reduced shard.
+//   copy engine (mode 2): the encoded shards are pulled from the peers' arenas
+//     into local staging and the reduced shard is pushed into the peers'
+//     arenas by the GPU's copy engines (cudaMemcpyAsync on peer-mapped
+//     memory); the owner kernel runs on local memory.  No SM is spent on the
+//     wire, so the codec kernels of neighbouring chunks overlap it freely.
 // No kernel here spins on memory another rank writes: ordering between ranks
 // comes only from collectives enqueued on the stream.
 #include "reduce_kernels.cuh"
@@ -103,7 +108,29 @@ struct Group {
     int device = 0;
     ncclComm_t comm = nullptr;
     double* scratch = nullptr;     // [0] shard sum of squares, [1] shard flag, [2] barrier token
+    // copy-engine transport: two streams that carry the peer copies, and the
+    // events that tie them to the caller's stream
+    cudaStream_t wire[2] = {nullptr, nullptr};
+    cudaEvent_t fork = nullptr;
+    cudaEvent_t join[2] = {nullptr, nullptr};
 };
+
+// Makes both wire streams wait for everything enqueued on `stream` so far.
+cudaError_t fork_wire(Group* g, cudaStream_t stream) {
+    cudaError_t e = cudaEventRecord(g->fork, stream);
+    for (int w = 0; e == cudaSuccess && w < 2; ++w) e = cudaStreamWaitEvent(g->wire[w], g->fork, 0);
+    return e;
+}
+
+// Makes `stream` wait for everything enqueued on the wire streams so far.
+cudaError_t join_wire(Group* g, cudaStream_t stream) {
+    cudaError_t e = cudaSuccess;
+    for (int w = 0; e == cudaSuccess && w < 2; ++w) {
+        e = cudaEventRecord(g->join[w], g->wire[w]);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(stream, g->join[w], 0);
+    }
+    return e;
+}
 
 constexpr int kPhaseBegin = 1;   // first chunk of a step: reset the group's partials
 constexpr int kPhaseEnd = 2;     // last chunk: fence + sum the partials over ranks, publish
@@ -232,6 +259,11 @@ NNTRAIN_EXPORT int nntrain_gradient_group_create(const void* id128, int world, i
     g->device = device;
     cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&g->scratch), 4 * sizeof(double));
     if (e == cudaSuccess) e = cudaMemset(g->scratch, 0, 4 * sizeof(double));
+    for (int w = 0; e == cudaSuccess && w < 2; ++w) {
+        e = cudaStreamCreateWithFlags(&g->wire[w], cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&g->join[w], cudaEventDisableTiming);
+    }
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&g->fork, cudaEventDisableTiming);
     if (e != cudaSuccess) { delete g; return static_cast<int>(e); }
     if (world > 1) {
         const NcclApi* api = nccl();
@@ -254,6 +286,11 @@ NNTRAIN_EXPORT int nntrain_gradient_group_destroy(void* group) {
         if (api) { int s = nccl_status(api->CommDestroy(g->comm)); if (first == 0) first = s; }
     }
     if (g->scratch) { int s = static_cast<int>(cudaFree(g->scratch)); if (first == 0) first = s; }
+    for (int w = 0; w < 2; ++w) {
+        if (g->wire[w]) { cudaStreamSynchronize(g->wire[w]); cudaStreamDestroy(g->wire[w]); }
+        if (g->join[w]) cudaEventDestroy(g->join[w]);
+    }
+    if (g->fork) cudaEventDestroy(g->fork);
     delete g;
     return first;
 }
@@ -350,20 +387,23 @@ NNTRAIN_EXPORT int nntrain_gradient_reduce_shards_bf16(
 // first chunk (reset the group's partials), bit 1 on the last (fence, sum the
 // partials over ranks, publish); 3 for a whole arena in one call.  Without
 // bit 1 the chunk's result must not be read before a later collective on the
-// group has completed (the next chunk's leading barrier is one).  mode 0 = peer memory, one fused kernel; mode 1 = NCCL send/recv
+// group has completed (the next chunk's leading barrier is one): when
+// `previous_final` is given it is recorded on `stream` right behind this
+// call's leading barrier, i.e. at the point where every EARLIER chunk of the
+// step is complete on this rank.  mode 0 = peer memory, one fused kernel; mode 2 = copy engines through the same staging; mode 1 = NCCL send/recv
 // through staging_payload / staging_scales (capacity: world shards).
 // Collective: every rank must call it with the same length / block / mode, in
 // the same order relative to other calls on the group.
 NNTRAIN_EXPORT int nntrain_gradient_allreduce_bfp8(
     void* group, signed char* const* payload_by_rank, float* const* scales_by_rank, long long length,
     int block_size, float reduction_scale, double* squared_sum, int* finite_status, int mode, int phase,
-    signed char* staging_payload, float* staging_scales, cudaStream_t stream) {
+    signed char* staging_payload, float* staging_scales, cudaEvent_t previous_final, cudaStream_t stream) {
     Group* g = static_cast<Group*>(group);
     if (!g || !payload_by_rank || !scales_by_rank || length <= 0 || !std::isfinite(reduction_scale) ||
-        (block_size != 32 && block_size != 64 && block_size != 128) || (mode != 0 && mode != 1) ||
+        (block_size != 32 && block_size != 64 && block_size != 128) || mode < 0 || mode > 2 ||
         phase < 0 || phase > 3)
         return static_cast<int>(cudaErrorInvalidValue);
-    if (mode == 1 && g->world > 1 && (!staging_payload || !staging_scales))
+    if (mode != 0 && g->world > 1 && (!staging_payload || !staging_scales))
         return static_cast<int>(cudaErrorInvalidValue);
     int status = select_device(g->device);
     if (status != cudaSuccess) return status;
@@ -384,6 +424,8 @@ NNTRAIN_EXPORT int nntrain_gradient_allreduce_bfp8(
     if (mode == 0 || world == 1) {
         // Every rank's encode must have finished before anyone reads it.
         if (world > 1 && (status = barrier(g, stream)) != 0) return status;
+        if (previous_final != nullptr && (e = cudaEventRecord(previous_final, stream)) != cudaSuccess)
+            return static_cast<int>(e);
         shards.outputs = world;
         for (int k = 0; k < world; ++k) {
             if (!payload_by_rank[k] || !scales_by_rank[k]) return static_cast<int>(cudaErrorInvalidValue);
@@ -398,9 +440,68 @@ NNTRAIN_EXPORT int nntrain_gradient_allreduce_bfp8(
                                             shard_flag, stream);
             if (e != cudaSuccess) return static_cast<int>(e);
         }
+    } else if (mode == 2) {
+        // Copy-engine transport: the SMs stay free for the codec kernels of
+        // the neighbouring chunks.  Pull my shard from every peer into staging,
+        // reduce locally, push the reduced shard into every peer's arena.  The
+        // leading barrier says every rank's encode of this chunk is done (and
+        // that the previous chunk's pushes have landed); the pushes of this
+        // chunk are fenced by the next collective on the group.
+        signed char* own_payload = payload_by_rank[rank];
+        float* own_scales = scales_by_rank[rank];
+        if (!own_payload || !own_scales) return static_cast<int>(cudaErrorInvalidValue);
+        for (int k = 0; k < world; ++k)
+            if (!payload_by_rank[k] || !scales_by_rank[k]) return static_cast<int>(cudaErrorInvalidValue);
+        const long long shard_scales = shard / block_size;
+        if ((status = barrier(g, stream)) != 0) return status;
+        if (previous_final != nullptr && (e = cudaEventRecord(previous_final, stream)) != cudaSuccess)
+            return static_cast<int>(e);
+        if (end > first) {
+            const long long sa = first / block_size, sb = (end + block_size - 1) / block_size;
+            if ((e = fork_wire(g, stream)) != cudaSuccess) return static_cast<int>(e);
+            for (int step = 1; step < world; ++step) {
+                const int peer = (rank + step) % world;
+                cudaStream_t lane = g->wire[step & 1];
+                e = cudaMemcpyAsync(staging_payload + shard * peer, payload_by_rank[peer] + first,
+                                    static_cast<size_t>(end - first), cudaMemcpyDeviceToDevice, lane);
+                if (e == cudaSuccess)
+                    e = cudaMemcpyAsync(staging_scales + shard_scales * peer, scales_by_rank[peer] + sa,
+                                        static_cast<size_t>(sb - sa) * sizeof(float), cudaMemcpyDeviceToDevice, lane);
+                if (e != cudaSuccess) return static_cast<int>(e);
+            }
+            if ((e = join_wire(g, stream)) != cudaSuccess) return static_cast<int>(e);
+            shards.outputs = 1;
+            for (int k = 0; k < world; ++k) {
+                if (k == rank) { shards.payload[k] = own_payload; shards.scales[k] = own_scales; }
+                else {
+                    shards.payload[k] = staging_payload + shard * k - first;
+                    shards.scales[k] = staging_scales + shard_scales * k - sa;
+                }
+            }
+            shards.out_payload[0] = own_payload;
+            shards.out_scales[0] = own_scales;
+            e = launch_bfp8_reduce_reencode(shards, first, end, block_size, reduction_scale, g->scratch,
+                                            shard_flag, stream);
+            if (e != cudaSuccess) return static_cast<int>(e);
+            if ((e = fork_wire(g, stream)) != cudaSuccess) return static_cast<int>(e);
+            for (int step = 1; step < world; ++step) {
+                const int peer = (rank + step) % world;
+                cudaStream_t lane = g->wire[step & 1];
+                e = cudaMemcpyAsync(payload_by_rank[peer] + first, own_payload + first,
+                                    static_cast<size_t>(end - first), cudaMemcpyDeviceToDevice, lane);
+                if (e == cudaSuccess)
+                    e = cudaMemcpyAsync(scales_by_rank[peer] + sa, own_scales + sa,
+                                        static_cast<size_t>(sb - sa) * sizeof(float), cudaMemcpyDeviceToDevice, lane);
+                if (e != cudaSuccess) return static_cast<int>(e);
+            }
+            if ((e = join_wire(g, stream)) != cudaSuccess) return static_cast<int>(e);
+        }
     } else {
         const NcclApi* api = nccl();
         if (!api) return kNcclMissing;
+        // with send/recv every earlier chunk is already final in stream order
+        if (previous_final != nullptr && (e = cudaEventRecord(previous_final, stream)) != cudaSuccess)
+            return static_cast<int>(e);
         signed char* own_payload = payload_by_rank[rank];
         float* own_scales = scales_by_rank[rank];
         if (!own_payload || !own_scales) return static_cast<int>(cudaErrorInvalidValue);
@@ -565,4 +666,12 @@ NNTRAIN_EXPORT int nntrain_gradient_group_sum(void* group, double* values, int c
     const NcclApi* api = nccl();
     if (!api) return kNcclMissing;
     return nccl_status(api->AllReduce(values, values, static_cast<size_t>(count), ncclDouble, ncclSum, g->comm, stream));
+}
+
+// cudaStreamWaitEvent for hosts that hold only the opaque handles (the
+// reference's exchange entry points do this internally,
+// NNtrain.Cuda/native/gradient_collectives.cu:284-291).
+NNTRAIN_EXPORT int nntrain_gradient_stream_wait_event(cudaStream_t stream, cudaEvent_t event) {
+    if (!event) return static_cast<int>(cudaErrorInvalidValue);
+    return static_cast<int>(cudaStreamWaitEvent(stream, event, 0));
 }

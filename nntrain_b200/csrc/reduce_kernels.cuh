@@ -56,48 +56,181 @@ __device__ __forceinline__ void accumulate16(const uint4& words, float scale, fl
 // per input rank, one 128-bit payload store per destination); a block of
 // kBlock values is kBlock/16 adjacent lanes.  A warp step covers 512 values.
 // Requirements: all payload pointers 16-byte aligned, first_value a multiple
-// of 512 relative to an aligned base; the ragged end (< 512 values) is done
-// with scalar accesses by the same kernel, as is everything when vector_ok
-// is false.
-// kRanks > 0: number of inputs known at compile time (all loads issued before
-// the first use); kRanks == 0: runtime count.
+// of 16; the ragged end (< 512 values) is done with scalar accesses by the
+// same kernel, as is everything when vector_ok is false.
+// kRanks > 0: number of inputs known at compile time.  The loads of the NEXT
+// tile are issued before the current tile's arithmetic, so every warp always
+// has one tile of every rank in flight: with peer pointers that hides the
+// NVLink round trip even when only a few CTAs are given to the kernel.
+// kRanks == 0: runtime count, no prefetch.
+template <int kRanks>
+struct ShardTile {
+    uint4 words[kRanks > 0 ? kRanks : 1];
+    float scale[kRanks > 0 ? kRanks : 1];
+};
+
+template <int kBlock, int kRanks>
+__device__ __forceinline__ void load_shard_tile(const EncodedShards& shards, long long base, int lane,
+                                                ShardTile<kRanks>& tile) {
+    const long long at = base + lane * 16;
+    const long long block_index = at / kBlock;
+    #pragma unroll
+    for (int k = 0; k < kRanks; ++k) {
+        tile.words[k] = __ldcs(reinterpret_cast<const uint4*>(shards.payload[k] + at));
+        tile.scale[k] = __ldcs(shards.scales[k] + block_index);
+    }
+}
+
+// Re-encodes acc[16] (already summed and scaled) and stores payload + scale to
+// every destination.
+template <int kBlock, bool kSquares>
+__device__ __forceinline__ void reencode_and_store(const EncodedShards& shards, long long base, int lane,
+                                                   float (&acc)[16], float reduction_scale,
+                                                   double& squares, int& non_finite) {
+    constexpr int kLanesPerBlock = kBlock / 16;
+    const long long at = base + lane * 16;
+    float m = 0.0f;
+    #pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        acc[i] = __fmul_rn(reduction_scale, acc[i]);
+        non_finite |= is_non_finite(acc[i]);
+        m = fmaxf(m, fabsf(acc[i]));
+    }
+    m = group_max<kLanesPerBlock>(m);
+    // a NaN sum is dropped by fmaxf and an Inf one gives scale = Inf; both are
+    // flagged above and take the exact per-value path inside biased_codes_of
+    const float scale = scale_from_maximum_fast(m);
+    const BlockScale divisor = block_scale(scale);
+    float t[16];
+    #pragma unroll
+    for (int i = 0; i < 16; i += 4)
+        biased_codes_of(make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]), divisor,
+                        t[i], t[i + 1], t[i + 2], t[i + 3]);
+    uint4 packed;
+    packed.x = pack_codes(t[0], t[1], t[2], t[3]);
+    packed.y = pack_codes(t[4], t[5], t[6], t[7]);
+    packed.z = pack_codes(t[8], t[9], t[10], t[11]);
+    packed.w = pack_codes(t[12], t[13], t[14], t[15]);
+    if (kSquares) {
+        #pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const double d = static_cast<double>(__fmul_rn(code_value(t[i]), scale));
+            squares += d * d;
+        }
+    }
+    // Gather the tile's scales (one per kLanesPerBlock lanes) into the low
+    // lanes so each destination gets one contiguous store.
+    constexpr int kScalesPerTile = 512 / kBlock;
+    const float routed = __shfl_sync(0xffffffffu, scale, (lane * kLanesPerBlock) & 31);
+    for (int d = 0; d < shards.outputs; ++d) {
+        *reinterpret_cast<uint4*>(shards.out_payload[d] + at) = packed;
+        if (lane < kScalesPerTile) shards.out_scales[d][base / kBlock + lane] = routed;
+    }
+}
+
+// One (possibly partial) tile with scalar accesses: one block at a time, the
+// warp's lanes stride over it.
+template <int kBlock, bool kSquares>
+__device__ __forceinline__ void reduce_tile_scalar(const EncodedShards& shards, int ranks, long long base,
+                                                   long long end_value, int lane, float reduction_scale,
+                                                   double& squares, int& non_finite) {
+    const long long tile_end = base + 512 < end_value ? base + 512 : end_value;
+    for (long long start = base; start < tile_end; start += kBlock) {
+        const long long stop = start + kBlock < end_value ? start + kBlock : end_value;
+        const long long block_index = start / kBlock;
+        constexpr int kPerLane = kBlock / 32;
+        float value[kPerLane];
+        float m = 0.0f;
+        #pragma unroll
+        for (int e = 0; e < kPerLane; ++e) {
+            const long long i = start + lane + e * 32;
+            float sum = 0.0f;
+            if (i < stop) {
+                for (int k = 0; k < ranks; ++k) {
+                    const float s = shards.scales[k][block_index];
+                    non_finite |= bad_scale(s);
+                    const float term = __fmul_rn(static_cast<float>(shards.payload[k][i]), s);
+                    sum = k == 0 ? term : __fadd_rn(sum, term);
+                }
+                sum = __fmul_rn(reduction_scale, sum);
+                non_finite |= is_non_finite(sum);
+                m = fmaxf(m, fabsf(sum));
+            }
+            value[e] = sum;
+        }
+        m = group_max<32>(m);
+        const float scale = scale_from_maximum(m);
+        #pragma unroll
+        for (int e = 0; e < kPerLane; ++e) {
+            const long long i = start + lane + e * 32;
+            if (i < stop) {
+                const float t = biased_code_of(value[e], scale);
+                if (kSquares) {
+                    const double d = static_cast<double>(__fmul_rn(code_value(t), scale));
+                    squares += d * d;
+                }
+                for (int d = 0; d < shards.outputs; ++d) shards.out_payload[d][i] = code_byte(t);
+            }
+        }
+        if (lane == 0)
+            for (int d = 0; d < shards.outputs; ++d) shards.out_scales[d][block_index] = scale;
+    }
+}
+
+// At most 96 registers per thread: one 256-thread CTA per SM then leaves
+// room for three CTAs of a codec kernel working on the neighbouring chunk.
 template <int kBlock, int kRanks, bool kSquares>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __maxnreg__(96)
 bfp8_reduce_reencode_kernel(EncodedShards shards, long long first_value, long long end_value,
                             float reduction_scale, double* squared_sum, int* finite_status,
                             bool vector_ok) {
     static_assert(kBlock == 32 || kBlock == 64 || kBlock == 128, "fast path block sizes");
-    constexpr int kLanesPerBlock = kBlock / 16;
     const int ranks = kRanks > 0 ? kRanks : shards.inputs;
     const int lane = threadIdx.x & 31;
     const long long warp = static_cast<long long>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
     const long long warps = static_cast<long long>(gridDim.x) * kWarpsPerCta;
-    const long long span = end_value - first_value;
-    const long long tiles = (span + 511) / 512;
+    const long long tiles = (end_value - first_value + 511) / 512;
     double squares = 0.0;
     int non_finite = 0;
 
-    for (long long tile = warp; tile < tiles; tile += warps) {
-        const long long base = first_value + tile * 512;
-        if (vector_ok && base + 512 <= end_value) {
-            const long long at = base + lane * 16;
-            const long long block_index = at / kBlock;
-            float acc[16];
-            if (kRanks > 0) {
-                uint4 words[kRanks > 0 ? kRanks : 1];
-                float scale[kRanks > 0 ? kRanks : 1];
+    auto is_fast = [&](long long tile) {
+        return vector_ok && tile < tiles && first_value + tile * 512 + 512 <= end_value;
+    };
+
+    if (kRanks > 0) {
+        ShardTile<kRanks> current, next;
+        long long tile = warp;
+        bool current_fast = is_fast(tile);
+        if (current_fast) load_shard_tile<kBlock, kRanks>(shards, first_value + tile * 512, lane, current);
+        while (tile < tiles) {
+            const long long following = tile + warps;
+            const bool next_fast = is_fast(following);
+            if (next_fast) load_shard_tile<kBlock, kRanks>(shards, first_value + following * 512, lane, next);
+            const long long base = first_value + tile * 512;
+            if (current_fast) {
+                float acc[16];
                 #pragma unroll
                 for (int k = 0; k < kRanks; ++k) {
-                    words[k] = __ldcs(reinterpret_cast<const uint4*>(shards.payload[k] + at));
-                    scale[k] = __ldcs(shards.scales[k] + block_index);
+                    non_finite |= bad_scale(current.scale[k]);
+                    if (k == 0) accumulate16<true>(current.words[k], current.scale[k], acc);
+                    else accumulate16<false>(current.words[k], current.scale[k], acc);
                 }
-                #pragma unroll
-                for (int k = 0; k < kRanks; ++k) {
-                    non_finite |= bad_scale(scale[k]);
-                    if (k == 0) accumulate16<true>(words[k], scale[k], acc);
-                    else accumulate16<false>(words[k], scale[k], acc);
-                }
+                reencode_and_store<kBlock, kSquares>(shards, base, lane, acc, reduction_scale, squares, non_finite);
             } else {
+                reduce_tile_scalar<kBlock, kSquares>(shards, ranks, base, end_value, lane, reduction_scale,
+                                                     squares, non_finite);
+            }
+            current = next;
+            current_fast = next_fast;
+            tile = following;
+        }
+    } else {
+        for (long long tile = warp; tile < tiles; tile += warps) {
+            const long long base = first_value + tile * 512;
+            if (is_fast(tile)) {
+                const long long at = base + lane * 16;
+                const long long block_index = at / kBlock;
+                float acc[16];
                 for (int k = 0; k < ranks; ++k) {
                     const uint4 words = __ldcs(reinterpret_cast<const uint4*>(shards.payload[k] + at));
                     const float scale = __ldcs(shards.scales[k] + block_index);
@@ -105,88 +238,10 @@ bfp8_reduce_reencode_kernel(EncodedShards shards, long long first_value, long lo
                     if (k == 0) accumulate16<true>(words, scale, acc);
                     else accumulate16<false>(words, scale, acc);
                 }
-            }
-            float m = 0.0f;
-            #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                acc[i] = __fmul_rn(reduction_scale, acc[i]);
-                non_finite |= is_non_finite(acc[i]);
-                m = fmaxf(m, fabsf(acc[i]));
-            }
-            m = group_max<kLanesPerBlock>(m);
-            // a NaN sum is dropped by fmaxf and an Inf one gives scale = Inf;
-            // both are flagged above and take the exact per-value path below
-            const float scale = scale_from_maximum_fast(m);
-            const BlockScale divisor = block_scale(scale);
-            float t[16];
-            #pragma unroll
-            for (int i = 0; i < 16; i += 4)
-                biased_codes_of(make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]), divisor,
-                                t[i], t[i + 1], t[i + 2], t[i + 3]);
-            uint4 packed;
-            packed.x = pack_codes(t[0], t[1], t[2], t[3]);
-            packed.y = pack_codes(t[4], t[5], t[6], t[7]);
-            packed.z = pack_codes(t[8], t[9], t[10], t[11]);
-            packed.w = pack_codes(t[12], t[13], t[14], t[15]);
-            if (kSquares) {
-                #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const double d = static_cast<double>(__fmul_rn(code_value(t[i]), scale));
-                    squares += d * d;
-                }
-            }
-            // Gather the tile's scales (one per kLanesPerBlock lanes) into the
-            // low lanes so each destination gets one contiguous store.
-            constexpr int kScalesPerTile = 512 / kBlock;
-            const float routed = __shfl_sync(0xffffffffu, scale, (lane * kLanesPerBlock) & 31);
-            for (int d = 0; d < shards.outputs; ++d) {
-                *reinterpret_cast<uint4*>(shards.out_payload[d] + at) = packed;
-                if (lane < kScalesPerTile) shards.out_scales[d][base / kBlock + lane] = routed;
-            }
-        } else {
-            // Ragged end (or unaligned pointers): one block at a time, the
-            // warp's lanes stride over it.
-            const long long tile_end = base + 512 < end_value ? base + 512 : end_value;
-            for (long long start = base; start < tile_end; start += kBlock) {
-                const long long stop = start + kBlock < end_value ? start + kBlock : end_value;
-                const long long block_index = start / kBlock;
-                constexpr int kPerLane = kBlock / 32;
-                float value[kPerLane];
-                float m = 0.0f;
-                #pragma unroll
-                for (int e = 0; e < kPerLane; ++e) {
-                    const long long i = start + lane + e * 32;
-                    float sum = 0.0f;
-                    if (i < stop) {
-                        for (int k = 0; k < ranks; ++k) {
-                            const float s = shards.scales[k][block_index];
-                            non_finite |= bad_scale(s);
-                            const float term = __fmul_rn(static_cast<float>(shards.payload[k][i]), s);
-                            sum = k == 0 ? term : __fadd_rn(sum, term);
-                        }
-                        sum = __fmul_rn(reduction_scale, sum);
-                        non_finite |= is_non_finite(sum);
-                        m = fmaxf(m, fabsf(sum));
-                    }
-                    value[e] = sum;
-                }
-                m = group_max<32>(m);
-                const float scale = scale_from_maximum(m);
-                const BlockScale divisor = block_scale(scale);
-                #pragma unroll
-                for (int e = 0; e < kPerLane; ++e) {
-                    const long long i = start + lane + e * 32;
-                    if (i < stop) {
-                        const float t = biased_code_of(value[e], divisor);
-                        if (kSquares) {
-                            const double d = static_cast<double>(__fmul_rn(code_value(t), scale));
-                            squares += d * d;
-                        }
-                        for (int d = 0; d < shards.outputs; ++d) shards.out_payload[d][i] = code_byte(t);
-                    }
-                }
-                if (lane == 0)
-                    for (int d = 0; d < shards.outputs; ++d) shards.out_scales[d][block_index] = scale;
+                reencode_and_store<kBlock, kSquares>(shards, base, lane, acc, reduction_scale, squares, non_finite);
+            } else {
+                reduce_tile_scalar<kBlock, kSquares>(shards, ranks, base, end_value, lane, reduction_scale,
+                                                     squares, non_finite);
             }
         }
     }

@@ -23,9 +23,9 @@ from dataclasses import dataclass
 import torch
 
 from .library import check, load
-from .native import CudaBfp8Native, GradientNorm, _stream
+from .native import CudaBfp8Native, CudaGradientBuckets, GradientNorm, _stream
 
-PEER, NCCL = 0, 1
+PEER, NCCL, COPY_ENGINE = 0, 1, 2
 
 
 def shard_range(length: int, world: int, rank: int) -> tuple[int, int]:
@@ -198,7 +198,7 @@ class Bfp8ArenaAllReduce:
     def __init__(self, group: GradientGroup, elements: int, block_size: int = 32, mode: int = PEER,
                  chunk_elements: int | None = None, reduction_scale: float = 1.0,
                  write_fp32: bool = True, codec_iterations_per_cta: int | None = None,
-                 collective_ctas: int | None = None):
+                 collective_ctas: int | None = None, chunk_plan: list[int] | None = None):
         if block_size not in (32, 64, 128):
             raise ValueError("block size must be 32, 64 or 128")
         self.group, self.elements, self.block, self.mode = group, elements, block_size, mode
@@ -209,6 +209,23 @@ class Bfp8ArenaAllReduce:
             chunk_elements = elements
         else:
             chunk_elements = max(align, chunk_elements // align * align)
+        # `chunk_plan`: explicit chunk lengths instead of equal chunks, e.g. a
+        # short first chunk (the wire starts early), long middle chunks (few
+        # barriers) and a short last one (little decode left at the end).
+        if chunk_plan:
+            plan = [max(align, int(c) // align * align) for c in chunk_plan]
+            spans, start = [], 0
+            for length in plan:
+                if start >= elements:
+                    break
+                spans.append((start, min(start + length, elements)))
+                start += length
+            if start < elements:
+                spans.append((start, elements))
+            chunk_elements = max(b - a for a, b in spans)
+        else:
+            spans = [(a, min(a + chunk_elements, elements)) for a in range(0, elements, chunk_elements)]
+        self.spans = spans
         self.chunk = chunk_elements
         device = group.device
         self.scale_count = (elements + block_size - 1) // block_size
@@ -221,7 +238,7 @@ class Bfp8ArenaAllReduce:
             self.finite_status = torch.zeros(1, dtype=torch.int32, device=f"cuda:{device}")
             self.norm_and_coefficient = torch.zeros(2, dtype=torch.float32, device=f"cuda:{device}")
             self.staging_payload = self.staging_scales = None
-            if mode == NCCL and world > 1:
+            if mode != PEER and world > 1:
                 first, end = shard_range(min(self.chunk, elements), world, 0)
                 shard = end - first
                 shard = (shard + 511) // 512 * 512
@@ -231,11 +248,13 @@ class Bfp8ArenaAllReduce:
             # Overlap shape: with more than one chunk in flight the codec kernels
             # use short-lived CTAs and the all-reduce kernel a capped grid on a
             # high-priority stream, so the three stages share the SMs.
-            overlapped = world > 1 and self.chunk < elements
+            overlapped = world > 1 and len(self.spans) > 1
             if codec_iterations_per_cta is None:
                 codec_iterations_per_cta = 4 if overlapped else 0
             if collective_ctas is None:
-                collective_ctas = 2 * torch.cuda.get_device_properties(device).multi_processor_count if overlapped else 0
+                # (with the copy-engine transport the owner kernel is local and short: no cap)
+                capped = overlapped and mode == PEER
+                collective_ctas = 2 * torch.cuda.get_device_properties(device).multi_processor_count if capped else 0
             self.codec_iterations_per_cta, self.collective_ctas = codec_iterations_per_cta, collective_ctas
             check("gradient_configure", load().nntrain_gradient_configure(codec_iterations_per_cta, collective_ctas))
             self.compute_stream = torch.cuda.Stream(device)
@@ -243,7 +262,10 @@ class Bfp8ArenaAllReduce:
             self.decode_stream = torch.cuda.Stream(device)
             self.h2d_stream = torch.cuda.Stream(device)
             self.d2h_stream = torch.cuda.Stream(device)
-            chunks = (elements + self.chunk - 1) // self.chunk
+            chunks = len(self.spans)
+            # native events: recorded by the all-reduce entry point behind its
+            # leading barrier ("every earlier chunk is final here")
+            self.final_events = [CudaGradientBuckets.create_ready_event(device) for _ in range(chunks)]
             self.encoded = [torch.cuda.Event() for _ in range(chunks)]
             self.reduced = [torch.cuda.Event() for _ in range(chunks)]
             self.uploaded = [torch.cuda.Event() for _ in range(chunks)]
@@ -276,9 +298,8 @@ class Bfp8ArenaAllReduce:
         for stream in (self.compute_stream, self.communication_stream, self.h2d_stream, self.d2h_stream):
             stream.wait_event(ready)
         launches = 2
-        spans = [(start, min(start + self.chunk, self.elements)) for start in range(0, self.elements, self.chunk)]
+        spans = self.spans
         first_stream = self.communication_stream if world == 1 else self.compute_stream
-        pending = None      # chunk whose result becomes readable after the next collective
         for index, (start, stop) in enumerate(spans):
             src = gradient[start:stop]
             payload = self.payload[start:stop]
@@ -295,7 +316,7 @@ class Bfp8ArenaAllReduce:
                                             squared_sum=self.squared_sum, finite_status=self.finite_status,
                                             stream=self.communication_stream)
                 launches += 1
-                self._result_final(index, (start, stop), gradient, host_payload, decode=False)
+                self._result_final(index, gradient, host_payload, decode=False)
                 continue
             CudaBfp8Native.block_encode(device, src, payload, scales, self.block,
                                         finite_status=self.finite_status, stream=self.compute_stream)
@@ -303,24 +324,24 @@ class Bfp8ArenaAllReduce:
             self.communication_stream.wait_event(self.encoded[index])
             payload_table = _pointer_table([p + start for p in self.payload_buffer.pointers])
             scales_table = _pointer_table([p + 4 * (start // self.block) for p in self.scales_buffer.pointers])
-            phase = (1 if index == 0 else 0) | (2 if index == len(spans) - 1 else 0)
+            last = index == len(spans) - 1
+            phase = (1 if index == 0 else 0) | (2 if last else 0)
+            # A chunk's result is complete on every rank only after the NEXT
+            # collective on the group: this call records final_events[index - 1]
+            # right behind its leading barrier.
             check("gradient_allreduce_bfp8", lib.nntrain_gradient_allreduce_bfp8(
                 group.handle, payload_table, scales_table, stop - start, self.block, self.reduction_scale,
                 self.squared_sum.data_ptr(), self.finite_status.data_ptr(), self.mode, phase,
                 0 if self.staging_payload is None else self.staging_payload.data_ptr(),
                 0 if self.staging_scales is None else self.staging_scales.data_ptr(),
+                self.final_events[index - 1] if index > 0 else None,
                 self.communication_stream.cuda_stream))
             launches += 2 + (1 if phase & 1 else 0) + (2 if phase & 2 else 0)
-            # In peer mode a chunk's result is complete on every rank only
-            # after the NEXT collective on the group (the next chunk's leading
-            # barrier, or this chunk's own closing fence when it is the last).
-            if pending is not None:
-                launches += self._result_final(pending, spans[pending], gradient, host_payload, self.write_fp32)
-                pending = None
-            if self.mode == NCCL or phase & 2:
-                launches += self._result_final(index, (start, stop), gradient, host_payload, self.write_fp32)
-            else:
-                pending = index
+            if index > 0:
+                launches += self._result_final(index - 1, gradient, host_payload, self.write_fp32,
+                                               self.final_events[index - 1])
+            if last:
+                launches += self._result_final(index, gradient, host_payload, self.write_fp32)
         with torch.cuda.stream(self.communication_stream):
             if max_norm is not None:
                 GradientNorm.clip_coefficient(device, self.squared_sum, max_norm, self.norm_and_coefficient,
@@ -336,20 +357,28 @@ class Bfp8ArenaAllReduce:
         current.wait_stream(self.communication_stream)
         self.kernel_launches = launches
 
-    def _result_final(self, index: int, span, gradient, host_payload, decode: bool) -> int:
-        """Chunk `index` is final in stream order on the communication stream:
-        start its decode and its copy back to the host."""
-        start, stop = span
+    def _result_final(self, index: int, gradient, host_payload, decode: bool, native_event=None) -> int:
+        """Chunk `index` is final: behind `native_event` when given, else in
+        stream order on the communication stream.  Starts its decode and its
+        copy back to the host."""
+        start, stop = self.spans[index]
         if not decode and host_payload is None:
             return 0
-        self.reduced[index].record(self.communication_stream)
+        lib = load()
+        waiters = ([self.d2h_stream] if host_payload is not None else []) + ([self.decode_stream] if decode else [])
+        if native_event is None:
+            self.reduced[index].record(self.communication_stream)
+            for stream in waiters:
+                stream.wait_event(self.reduced[index])
+        else:
+            for stream in waiters:
+                check("gradient_stream_wait_event",
+                      lib.nntrain_gradient_stream_wait_event(stream.cuda_stream, native_event))
         if host_payload is not None:
-            self.d2h_stream.wait_event(self.reduced[index])
             with torch.cuda.stream(self.d2h_stream):
                 host_payload[start:stop].copy_(self.payload[start:stop], non_blocking=True)
         if not decode:
             return 0
-        self.decode_stream.wait_event(self.reduced[index])
         CudaBfp8Native.block_decode(self.group.device, self.payload[start:stop],
                                     self.scales[start // self.block:(stop + self.block - 1) // self.block],
                                     gradient[start:stop], self.block, stream=self.decode_stream)
@@ -372,6 +401,9 @@ class Bfp8ArenaAllReduce:
 
     def close(self) -> None:
         torch.cuda.synchronize(self.group.device)
+        for event in self.final_events:
+            CudaGradientBuckets.destroy_event(self.group.device, event)
+        self.final_events = []
         self.payload = self.scales = None
         self.payload_buffer.close()
         self.scales_buffer.close()

@@ -25,7 +25,7 @@ def main() -> None:
     group = reducers.GradientGroup(world, rank, local)
     failures = []
     cases = [(515, 32, None), (70001, 32, None), ((1 << 20) + 4096, 32, 1 << 18), (1 << 20, 128, None)]
-    for mode in (reducers.PEER, reducers.NCCL):
+    for mode in (reducers.PEER, reducers.COPY_ENGINE, reducers.NCCL):
         for n, block, chunk in cases:
             gradients = [oracle.generate_gradient(n, 0xB2000000 + n, r) for r in range(world)]
             scale = 1.0 / world

@@ -62,6 +62,7 @@ def parse_args():
     p.add_argument("--chunk-plan", default="", help="comma-separated chunk lengths in Mi values (overrides --chunk-elements)")
     p.add_argument("--codec-iterations", type=int, default=-1, help="-1 = library default for the run")
     p.add_argument("--collective-ctas", type=int, default=-1, help="-1 = library default for the run")
+    p.add_argument("--collective-async", type=int, default=1, help="1 = cp.async ring all-reduce kernel, 0 = register prefetch")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--cpu-sample-elements", type=int, default=64 << 20)
@@ -250,6 +251,8 @@ def time_kernels(args):
     from nntrain_b200.native import CudaBfp8Native, CudaGradientBuckets, GradientNorm
 
     torch.cuda.set_device(0)
+    from nntrain_b200.library import load
+    load().nntrain_gradient_configure_collective(args.collective_async)
     E = min(args.elements, 256 << 20)
     peak, kind = measured_peaks()
     arena = torch.empty(E, dtype=torch.float32, device="cuda")
@@ -334,7 +337,7 @@ def time_phases(args, step, arena, world, rank, local_rank, barrier):
             step.group.handle, table_p, table_s, E, BLOCK, 1.0 / world, step.squared_sum.data_ptr(),
             step.finite_status.data_ptr(), step.mode, 3,
             0 if step.staging_payload is None else step.staging_payload.data_ptr(),
-            0 if step.staging_scales is None else step.staging_scales.data_ptr(), stream.cuda_stream))
+            0 if step.staging_scales is None else step.staging_scales.data_ptr(), None, stream.cuda_stream))
 
     def decode():
         CudaBfp8Native.block_decode(local_rank, step.payload, step.scales, arena, BLOCK)
@@ -384,6 +387,7 @@ def main():
     from nntrain_b200 import reducers
     from nntrain_b200.library import load
     load()      # fails loudly when the CUDA library is missing
+    load().nntrain_gradient_configure_collective(args.collective_async)
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)

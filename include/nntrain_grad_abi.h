@@ -71,6 +71,10 @@ int nntrain_cuda_use_external_stream(void* stream);
  * collective_ctas: 0 = the all-reduce kernels fill the machine, n > 0 = at most
  * n CTAs.  Process-wide. */
 int nntrain_gradient_configure(int codec_iterations_per_cta, int collective_ctas);
+/* ABI minor 36; no counterpart in the reference.  How the all-reduce kernels
+ * fetch their inputs: 1 (default) = cp.async rings in shared memory, 0 =
+ * register prefetch.  Same results either way. */
+int nntrain_gradient_configure_collective(int asynchronous_copies);
 
 /* ---- BFP8 block codec ---------------------------------------------------
  * payload: signed int8 per value; scales: one fp32 per block,

@@ -26,6 +26,7 @@ int g_sm_counts[kMaxDevices] = {};
 
 std::atomic<int> g_codec_iterations_per_cta{0};
 std::atomic<int> g_collective_ctas{0};
+std::atomic<int> g_collective_async{1};
 
 }  // namespace
 
@@ -51,8 +52,11 @@ cudaStream_t& implicit_stream() { return t_implicit_stream; }
 
 LaunchPolicy launch_policy() {
     return LaunchPolicy{g_codec_iterations_per_cta.load(std::memory_order_relaxed),
-                        g_collective_ctas.load(std::memory_order_relaxed)};
+                        g_collective_ctas.load(std::memory_order_relaxed),
+                        g_collective_async.load(std::memory_order_relaxed)};
 }
+
+void set_collective_async(int enabled) { g_collective_async.store(enabled ? 1 : 0, std::memory_order_relaxed); }
 
 void set_launch_policy(int codec_iterations_per_cta, int collective_ctas) {
     g_codec_iterations_per_cta.store(codec_iterations_per_cta, std::memory_order_relaxed);
@@ -138,6 +142,14 @@ NNTRAIN_EXPORT int nntrain_cuda_set_device(int device) {
 NNTRAIN_EXPORT int nntrain_gradient_configure(int codec_iterations_per_cta, int collective_ctas) {
     if (codec_iterations_per_cta < 0 || collective_ctas < 0) return static_cast<int>(cudaErrorInvalidValue);
     set_launch_policy(codec_iterations_per_cta, collective_ctas);
+    return static_cast<int>(cudaSuccess);
+}
+
+// Chooses how the all-reduce kernels fetch their inputs (ABI minor 36, no
+// counterpart in the reference): 1 (default) = cp.async rings in shared
+// memory, 0 = register prefetch.  Same results either way.
+NNTRAIN_EXPORT int nntrain_gradient_configure_collective(int asynchronous_copies) {
+    set_collective_async(asynchronous_copies);
     return static_cast<int>(cudaSuccess);
 }
 

@@ -74,9 +74,11 @@ int sm_count();
 struct LaunchPolicy {
     int codec_iterations_per_cta;
     int collective_ctas;
+    int collective_async;     // 1: all-reduce kernels stage their inputs with cp.async rings
 };
 LaunchPolicy launch_policy();
 void set_launch_policy(int codec_iterations_per_cta, int collective_ctas);
+void set_collective_async(int enabled);
 
 // Grid for `work_items` CTA-sized loop iterations: persistent (fill every SM
 // `per_sm` times, never more than the work needs) or, under the policy above,

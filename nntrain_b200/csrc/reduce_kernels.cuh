@@ -251,6 +251,98 @@ bfp8_reduce_reencode_kernel(EncodedShards shards, long long first_value, long lo
     if (kSquares) cta_accumulate(squares, squared_sum);
 }
 
+// ---- asynchronous-copy variant ------------------------------------------------
+// Same arithmetic; the inputs travel global -> shared memory with cp.async
+// (16-byte payload pieces, 4-byte scales) through a ring of kStages tiles per
+// warp.  Every lane copies exactly the bytes it will consume, so completion is
+// tracked by the lane's own cp.async groups (wait_group is a scoreboard wait:
+// nothing here can spin forever) and no cross-lane synchronisation is needed.
+// The bytes in flight live in shared memory, not in registers: a single
+// 256-thread CTA per SM keeps kStages - 1 tiles of every rank outstanding
+// (N = 8: 3 x 4.6 KB per warp, 110 KB per SM), which rides out the longer
+// NVLink / HBM latency seen while codec kernels saturate the memory system,
+// and leaves most of the register file to those kernels.
+__device__ __forceinline__ void async_copy_16(void* shared_destination, const void* source) {
+    const unsigned address = static_cast<unsigned>(__cvta_generic_to_shared(shared_destination));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(address), "l"(source) : "memory");
+}
+__device__ __forceinline__ void async_copy_4(void* shared_destination, const void* source) {
+    const unsigned address = static_cast<unsigned>(__cvta_generic_to_shared(shared_destination));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(address), "l"(source) : "memory");
+}
+__device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory"); }
+
+template <int kRanks, int kStages>
+constexpr size_t reduce_ring_bytes() {
+    return static_cast<size_t>(kWarpsPerCta) * kStages * kRanks * 32 * (sizeof(uint4) + sizeof(float));
+}
+
+template <int kBlock, int kRanks, bool kSquares, int kStages>
+__global__ void __launch_bounds__(kThreads)
+bfp8_reduce_reencode_async_kernel(EncodedShards shards, long long first_value, long long end_value,
+                                  float reduction_scale, double* squared_sum, int* finite_status) {
+    static_assert(kRanks > 0 && kStages >= 2, "compile-time rank count, at least two stages");
+    extern __shared__ uint4 ring[];
+    const int lane = threadIdx.x & 31;
+    const int warp_in_cta = threadIdx.x >> 5;
+    // payload ring: [warp][stage][rank][lane] uint4; scale ring behind it: same shape, float
+    uint4* payload_ring = ring + static_cast<size_t>(warp_in_cta) * kStages * kRanks * 32;
+    float* scale_ring = reinterpret_cast<float*>(ring + static_cast<size_t>(kWarpsPerCta) * kStages * kRanks * 32) +
+                        static_cast<size_t>(warp_in_cta) * kStages * kRanks * 32;
+    const long long warp = static_cast<long long>(blockIdx.x) * kWarpsPerCta + warp_in_cta;
+    const long long warps = static_cast<long long>(gridDim.x) * kWarpsPerCta;
+    const long long tiles = (end_value - first_value + 511) / 512;
+    double squares = 0.0;
+    int non_finite = 0;
+
+    auto is_fast = [&](long long tile) { return tile < tiles && first_value + tile * 512 + 512 <= end_value; };
+    auto issue = [&](long long tile, int stage) {
+        if (is_fast(tile)) {
+            const long long at = first_value + tile * 512 + lane * 16;
+            const long long block_index = at / kBlock;
+            #pragma unroll
+            for (int k = 0; k < kRanks; ++k) {
+                async_copy_16(payload_ring + (stage * kRanks + k) * 32 + lane, shards.payload[k] + at);
+                async_copy_4(scale_ring + (stage * kRanks + k) * 32 + lane, shards.scales[k] + block_index);
+            }
+        }
+        async_commit();      // one group per tile slot, empty when there is nothing to copy
+    };
+
+    #pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) issue(warp + s * warps, s);
+    int stage = 0;
+    for (long long tile = warp; tile < tiles; tile += warps) {
+        // The slot being refilled was consumed in the previous iteration.
+        issue(tile + (kStages - 1) * warps, (stage + kStages - 1) % kStages);
+        async_wait<kStages - 1>();
+        const long long base = first_value + tile * 512;
+        if (is_fast(tile)) {
+            float acc[16];
+            #pragma unroll
+            for (int k = 0; k < kRanks; ++k) {
+                const uint4 words = payload_ring[(stage * kRanks + k) * 32 + lane];
+                const float scale = scale_ring[(stage * kRanks + k) * 32 + lane];
+                non_finite |= bad_scale(scale);
+                if (k == 0) accumulate16<true>(words, scale, acc);
+                else accumulate16<false>(words, scale, acc);
+            }
+            reencode_and_store<kBlock, kSquares>(shards, base, lane, acc, reduction_scale, squares, non_finite);
+        } else {
+            reduce_tile_scalar<kBlock, kSquares>(shards, kRanks, base, end_value, lane, reduction_scale,
+                                                 squares, non_finite);
+        }
+        stage = (stage + 1) % kStages;
+    }
+    async_wait<0>();
+    if (finite_status != nullptr) {
+        if (__any_sync(0xffffffffu, non_finite) && lane == 0) atomicExch(finite_status, 1);
+    }
+    if (kSquares) cta_accumulate(squares, squared_sum);
+}
+
 // N encoded inputs -> fp32 sum, rank order, optional x reduction_scale,
 // optional sum of squares of the fp32 result, optional finite flag with the
 // tensor-wide reducer's rule: an invalid input scale or a non-finite result

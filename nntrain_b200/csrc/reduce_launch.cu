@@ -24,10 +24,48 @@ cudaError_t run_reencode(const EncodedShards& shards, long long first_value, lon
     return cudaPeekAtLastError();
 }
 
+// cp.async ring variant: needs 16-byte aligned arenas and a compile-time rank
+// count.  One CTA per SM when it runs beside codec kernels; alone it may use
+// as many CTAs as the ring's shared memory lets an SM hold.
+template <int kBlock, int kRanks, int kStages>
+cudaError_t run_reencode_async(const EncodedShards& shards, long long first_value, long long end_value,
+                               float reduction_scale, double* squared_sum, int* finite_status,
+                               cudaStream_t stream) {
+    constexpr size_t bytes = reduce_ring_bytes<kRanks, kStages>();
+    const long long tiles = (end_value - first_value + 511) / 512;
+    const long long work = (tiles + kWarpsPerCta - 1) / kWarpsPerCta;
+    long long cap = launch_policy().collective_ctas;
+    if (cap <= 0) cap = static_cast<long long>(sm_count()) * (bytes > 100 * 1024 ? 1 : 2);
+    const int grid = static_cast<int>(work < cap ? work : cap);
+    cudaError_t e;
+    if (squared_sum != nullptr) {
+        auto kernel = bfp8_reduce_reencode_async_kernel<kBlock, kRanks, true, kStages>;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+        if (e != cudaSuccess) return e;
+        kernel<<<grid, kThreads, bytes, stream>>>(shards, first_value, end_value, reduction_scale, squared_sum,
+                                                 finite_status);
+    } else {
+        auto kernel = bfp8_reduce_reencode_async_kernel<kBlock, kRanks, false, kStages>;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+        if (e != cudaSuccess) return e;
+        kernel<<<grid, kThreads, bytes, stream>>>(shards, first_value, end_value, reduction_scale, nullptr,
+                                                 finite_status);
+    }
+    return cudaPeekAtLastError();
+}
+
 template <int kBlock>
 cudaError_t dispatch_reencode(const EncodedShards& shards, long long first_value, long long end_value,
                               float reduction_scale, double* squared_sum, int* finite_status,
                               bool vector_ok, cudaStream_t stream) {
+    if (vector_ok && launch_policy().collective_async) {
+        switch (shards.inputs) {
+            case 2: return run_reencode_async<kBlock, 2, 8>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, stream);
+            case 4: return run_reencode_async<kBlock, 4, 6>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, stream);
+            case 8: return run_reencode_async<kBlock, 8, 4>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, stream);
+            default: break;
+        }
+    }
     switch (shards.inputs) {
         case 2: return run_reencode<kBlock, 2>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, stream);
         case 4: return run_reencode<kBlock, 4>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, stream);

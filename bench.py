@@ -63,6 +63,7 @@ def parse_args():
     p.add_argument("--codec-iterations", type=int, default=-1, help="-1 = library default for the run")
     p.add_argument("--collective-ctas", type=int, default=-1, help="-1 = library default for the run")
     p.add_argument("--collective-async", type=int, default=1, help="1 = cp.async ring all-reduce kernel, 0 = register prefetch")
+    p.add_argument("--codec-ctas", type=int, default=0, help="cap on persistent codec grids (0 = none)")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--cpu-sample-elements", type=int, default=64 << 20)
@@ -252,7 +253,7 @@ def time_kernels(args):
 
     torch.cuda.set_device(0)
     from nntrain_b200.library import load
-    load().nntrain_gradient_configure_collective(args.collective_async)
+    load().nntrain_gradient_configure_collective(args.collective_async | (args.codec_ctas << 8))
     E = min(args.elements, 256 << 20)
     peak, kind = measured_peaks()
     arena = torch.empty(E, dtype=torch.float32, device="cuda")

@@ -27,6 +27,7 @@ int g_sm_counts[kMaxDevices] = {};
 std::atomic<int> g_codec_iterations_per_cta{0};
 std::atomic<int> g_collective_ctas{0};
 std::atomic<int> g_collective_async{1};
+std::atomic<int> g_codec_ctas{0};
 
 }  // namespace
 
@@ -53,8 +54,11 @@ cudaStream_t& implicit_stream() { return t_implicit_stream; }
 LaunchPolicy launch_policy() {
     return LaunchPolicy{g_codec_iterations_per_cta.load(std::memory_order_relaxed),
                         g_collective_ctas.load(std::memory_order_relaxed),
-                        g_collective_async.load(std::memory_order_relaxed)};
+                        g_collective_async.load(std::memory_order_relaxed),
+                        g_codec_ctas.load(std::memory_order_relaxed)};
 }
+
+void set_codec_ctas(int ctas) { g_codec_ctas.store(ctas > 0 ? ctas : 0, std::memory_order_relaxed); }
 
 void set_collective_async(int enabled) { g_collective_async.store(enabled ? 1 : 0, std::memory_order_relaxed); }
 
@@ -147,9 +151,11 @@ NNTRAIN_EXPORT int nntrain_gradient_configure(int codec_iterations_per_cta, int 
 
 // Chooses how the all-reduce kernels fetch their inputs (ABI minor 36, no
 // counterpart in the reference): 1 (default) = cp.async rings in shared
-// memory, 0 = register prefetch.  Same results either way.
+// memory, 0 = register prefetch.  Same results either way.  Bits 8 and up:
+// when non-zero, the cap on the CTAs of a persistent codec grid.
 NNTRAIN_EXPORT int nntrain_gradient_configure_collective(int asynchronous_copies) {
-    set_collective_async(asynchronous_copies);
+    set_collective_async(asynchronous_copies & 1);
+    set_codec_ctas(asynchronous_copies >> 8);
     return static_cast<int>(cudaSuccess);
 }
 

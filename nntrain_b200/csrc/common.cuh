@@ -68,6 +68,9 @@ int sm_count();
 //       alone.  n > 0: every CTA does n loop iterations and retires, so that a
 //       kernel on another stream (the collective) finds free SM slots while a
 //       codec kernel runs.
+//   codec_ctas  n > 0 (with codec_iterations_per_cta == 0): persistent codec
+//       grids of at most n CTAs, which bounds the share of HBM bandwidth and
+//       of SM slots a codec kernel takes while the collective runs.
 //   collective_ctas  0: the all-reduce kernels also fill the machine.  n > 0:
 //       they use at most n CTAs and leave the rest of the SMs' capacity to the
 //       codec kernels of the neighbouring chunks.
@@ -75,10 +78,12 @@ struct LaunchPolicy {
     int codec_iterations_per_cta;
     int collective_ctas;
     int collective_async;     // 1: all-reduce kernels stage their inputs with cp.async rings
+    int codec_ctas;           // > 0: persistent codec grids of at most this many CTAs
 };
 LaunchPolicy launch_policy();
 void set_launch_policy(int codec_iterations_per_cta, int collective_ctas);
 void set_collective_async(int enabled);
+void set_codec_ctas(int ctas);
 
 // Grid for `work_items` CTA-sized loop iterations: persistent (fill every SM
 // `per_sm` times, never more than the work needs) or, under the policy above,
@@ -90,7 +95,9 @@ inline int grid_for(long long work_items, int per_sm) {
         const long long ctas = (work_items + iterations - 1) / iterations;
         return static_cast<int>(ctas < 2147483647ll ? ctas : 2147483647ll);
     }
-    const long long cap = static_cast<long long>(sm_count()) * per_sm;
+    long long cap = static_cast<long long>(sm_count()) * per_sm;
+    const int limit = launch_policy().codec_ctas;
+    if (limit > 0 && limit < cap) cap = limit;
     return static_cast<int>(work_items < cap ? work_items : cap);
 }
 

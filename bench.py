@@ -62,7 +62,8 @@ def parse_args():
     p.add_argument("--chunk-plan", default="", help="comma-separated chunk lengths in Mi values (overrides --chunk-elements)")
     p.add_argument("--codec-iterations", type=int, default=-1, help="-1 = library default for the run")
     p.add_argument("--collective-ctas", type=int, default=-1, help="-1 = library default for the run")
-    p.add_argument("--collective-async", type=int, default=1, help="1 = cp.async ring all-reduce kernel, 0 = register prefetch")
+    p.add_argument("--collective-async", type=int, default=-1,
+                   help="1 = cp.async ring all-reduce kernel, 0 = register prefetch, -1 = library default for the run")
     p.add_argument("--codec-ctas", type=int, default=0, help="cap on persistent codec grids (0 = none)")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-cpu-baseline", action="store_true")
@@ -253,7 +254,8 @@ def time_kernels(args):
 
     torch.cuda.set_device(0)
     from nntrain_b200.library import load
-    load().nntrain_gradient_configure_collective(args.collective_async | (args.codec_ctas << 8))
+    if args.collective_async >= 0:
+        load().nntrain_gradient_configure_collective(args.collective_async)
     E = min(args.elements, 256 << 20)
     peak, kind = measured_peaks()
     arena = torch.empty(E, dtype=torch.float32, device="cuda")
@@ -388,7 +390,6 @@ def main():
     from nntrain_b200 import reducers
     from nntrain_b200.library import load
     load()      # fails loudly when the CUDA library is missing
-    load().nntrain_gradient_configure_collective(args.collective_async)
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
@@ -397,13 +398,16 @@ def main():
 
     E = args.elements
     mode = {"peer": reducers.PEER, "nccl": reducers.NCCL, "copy": reducers.COPY_ENGINE}[args.mode]
-    chunk = args.chunk_elements or (0 if world == 1 else 128 << 20)
+    chunk = args.chunk_elements      # 0: the library's default chunk plan
     group = reducers.GradientGroup(world, rank, local_rank)
     shape = dict(codec_iterations_per_cta=None if args.codec_iterations < 0 else args.codec_iterations,
                  collective_ctas=None if args.collective_ctas < 0 else args.collective_ctas,
-                 chunk_plan=[int(float(c) * (1 << 20)) for c in args.chunk_plan.split(",")] if args.chunk_plan else None)
+                 chunk_plan=[int(float(c) * (1 << 20)) for c in args.chunk_plan.split(",")] if args.chunk_plan else None,
+                 collective_async=None if args.collective_async < 0 else args.collective_async)
     step = reducers.Bfp8ArenaAllReduce(group, E, BLOCK, mode, chunk_elements=chunk or None,
                                        reduction_scale=1.0 / world, write_fp32=True, **shape)
+    if args.codec_ctas:
+        load().nntrain_gradient_configure_collective(step.collective_async | (args.codec_ctas << 8))
     device_chunks = [b - a for a, b in step.spans]
     device_chunk, device_shape = step.chunk, (step.codec_iterations_per_cta, step.collective_ctas)
     arena = torch.empty(E, dtype=torch.float32, device=device)
@@ -490,7 +494,7 @@ def main():
             step.close()
             e2e_step = reducers.Bfp8ArenaAllReduce(group, E, BLOCK, mode, chunk_elements=e2e_chunk,
                                                    reduction_scale=1.0 / world, write_fp32=True,
-                                                   **{**shape, "chunk_plan": None})
+                                                   **{**shape, "chunk_plan": None, "collective_async": None})
         e2e_steps = max(1, min(args.steps, 5))
         for _ in range(min(args.warmup, 2)):
             e2e_step.enqueue(arena, MAX_NORM, host_gradient, host_payload, host_scales)
@@ -539,7 +543,8 @@ def main():
                        "elements_per_rank": E, "block": BLOCK, "max_norm": MAX_NORM,
                        "transport": args.mode if world > 1 else "none (single-GPU publication)",
                        "chunk_elements": device_chunk, "chunks": device_chunks, "codec_iterations_per_cta": device_shape[0],
-                       "collective_ctas": device_shape[1], "reduction": "mean (reduction_scale 1/N)",
+                       "collective_ctas": device_shape[1], "collective_async": step.collective_async,
+                       "reduction": "mean (reduction_scale 1/N)",
                        "l2": "inputs (6.2 GB per rank) exceed the 126 MB L2; no flush needed",
                        "fp32_result": "arena overwritten with decode(encode(sum)) every step"},
             "algbw_gbs": algbw, "busbw_gbs": busbw,

@@ -198,7 +198,8 @@ class Bfp8ArenaAllReduce:
     def __init__(self, group: GradientGroup, elements: int, block_size: int = 32, mode: int = PEER,
                  chunk_elements: int | None = None, reduction_scale: float = 1.0,
                  write_fp32: bool = True, codec_iterations_per_cta: int | None = None,
-                 collective_ctas: int | None = None, chunk_plan: list[int] | None = None):
+                 collective_ctas: int | None = None, chunk_plan: list[int] | None = None,
+                 collective_async: int | None = None):
         if block_size not in (32, 64, 128):
             raise ValueError("block size must be 32, 64 or 128")
         self.group, self.elements, self.block, self.mode = group, elements, block_size, mode
@@ -212,6 +213,11 @@ class Bfp8ArenaAllReduce:
         # `chunk_plan`: explicit chunk lengths instead of equal chunks, e.g. a
         # short first chunk (the wire starts early), long middle chunks (few
         # barriers) and a short last one (little decode left at the end).
+        if chunk_plan is None and chunk_elements == elements and world > 1 and elements >= (64 << 20):
+            # default for a large arena: short first chunk (the wire starts
+            # early), long middle chunks (few barriers), short last chunks
+            # (little decode left when the wire is done)
+            chunk_plan = [int(elements * f) for f in (0.03, 0.10, 0.26, 0.26, 0.20, 0.09)]
         if chunk_plan:
             plan = [max(align, int(c) // align * align) for c in chunk_plan]
             spans, start = [], 0
@@ -254,9 +260,15 @@ class Bfp8ArenaAllReduce:
             if collective_ctas is None:
                 # (with the copy-engine transport the owner kernel is local and short: no cap)
                 capped = overlapped and mode == PEER
-                collective_ctas = 2 * torch.cuda.get_device_properties(device).multi_processor_count if capped else 0
+                collective_ctas = torch.cuda.get_device_properties(device).multi_processor_count if capped else 0
             self.codec_iterations_per_cta, self.collective_ctas = codec_iterations_per_cta, collective_ctas
             check("gradient_configure", load().nntrain_gradient_configure(codec_iterations_per_cta, collective_ctas))
+            # Measured on 8 x B200: beside codec kernels the register-prefetch
+            # kernel does better; alone, the cp.async ring does.
+            if collective_async is None:
+                collective_async = 0 if overlapped else 1
+            self.collective_async = collective_async
+            check("gradient_configure_collective", load().nntrain_gradient_configure_collective(collective_async))
             self.compute_stream = torch.cuda.Stream(device)
             self.communication_stream = torch.cuda.Stream(device, priority=-1)
             self.decode_stream = torch.cuda.Stream(device)

@@ -276,6 +276,22 @@ int nntrain_gradient_reduce_shards_bfp8(
     signed char* const* out_payloads, float* const* out_scales, long long first_value,
     long long end_value, int block_size, float reduction_scale, double* squared_sum,
     int* finite_status, nntrain_stream_t stream);
+/* No counterpart in the reference.  nntrain_gradient_reduce_shards_bfp8 for
+ * hosts that must not allocate device memory where they reduce (inside a
+ * pool that forbids foreign allocations, while a step is recorded for replay,
+ * in a loop that must stay off the allocator): same arguments and results,
+ * but the per-span sums of squares and the flag word live in a fixed 128 KiB
+ * array inside the library image, and no allocating routine is called.  The
+ * sum of squares is added in a fixed order (reproducible).  At most 2^30
+ * values per call: longer ranges return cudaErrorInvalidValue (error ring
+ * operation 200).  The first call on a device looks up the array's device
+ * address; make it before any stream capture starts there.  All calls on a
+ * GPU share the array: calls whose kernels overlap on that GPU race. */
+int nntrain_gradient_reduce_shards_bfp8_no_alloc(
+    int device, int inputs, const signed char* const* payloads, const float* const* scales, int outputs,
+    signed char* const* out_payloads, float* const* out_scales, long long first_value,
+    long long end_value, int block_size, float reduction_scale, double* squared_sum,
+    int* finite_status, nntrain_stream_t stream);
 /* bf16 twin (extends NNtrain.Cuda/native/gradient_collectives.cu:62-90). */
 int nntrain_gradient_reduce_shards_bf16(
     int device, int inputs, const unsigned short* const* values, int outputs,

@@ -52,6 +52,21 @@ def reduce_shards_bfp8(device: int, payloads, scales, out_payloads, out_scales, 
         0 if finite_status is None else finite_status.data_ptr(), _stream(stream)))
 
 
+def reduce_shards_bfp8_no_alloc(device: int, payloads, scales, out_payloads, out_scales, first: int, end: int,
+                                block_size: int, reduction_scale: float = 1.0, squared_sum=None,
+                                finite_status=None, stream=None) -> None:
+    """`reduce_shards_bfp8` for a host that may not allocate device memory at
+    this point: its scratch is a fixed array inside the library (at most 2^30
+    values per call; calls that overlap on one GPU race on that array)."""
+    check("gradient_reduce_shards_bfp8_no_alloc", load().nntrain_gradient_reduce_shards_bfp8_no_alloc(
+        device, len(payloads), _pointer_table([t.data_ptr() for t in payloads]),
+        _pointer_table([t.data_ptr() for t in scales]), len(out_payloads),
+        _pointer_table([t.data_ptr() for t in out_payloads]),
+        _pointer_table([t.data_ptr() for t in out_scales]), first, end, block_size, reduction_scale,
+        0 if squared_sum is None else squared_sum.data_ptr(),
+        0 if finite_status is None else finite_status.data_ptr(), _stream(stream)))
+
+
 def reduce_shards_bf16(device: int, values, out_values, reduced, first: int, end: int,
                        reduction_scale: float = 1.0, squared_sum=None, square_of_bf16: bool = True,
                        stream=None) -> None:

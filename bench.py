@@ -46,8 +46,9 @@ NVLINK_PER_DIRECTION_GBS = 900.0          # nominal, per GPU per direction
 NVLINK_MEASURED_PEER_COPY_GBS = 770.0     # measured peer copy on this pool
 # DRAM bytes per value of the dominant kernel (encode + write-back + sum of
 # squares) from the ncu capture summarised in
-# profiles/bfp8_encode_block32_publish_64Mi.md; None until captured.
-ENCODE_PUBLISH_DRAM_BYTES_PER_VALUE = None
+# profiles/bfp8_encode_block32_publish_64Mi.md (64 Mi-value launch, scaled by
+# the value count; ~0.7 B/value of writes were still in L2 at kernel end).
+ENCODE_PUBLISH_DRAM_BYTES_PER_VALUE = 8.43
 
 
 def parse_args():

@@ -66,8 +66,9 @@ int nntrain_cuda_use_external_stream(void* stream);
 
 /* ABI minor 36; no counterpart in the reference (its kernels use fixed
  * grids).  Launch shapes for overlapping the collective with the codec kernels
- * of neighbouring chunks.  codec_iterations_per_cta: 0 = persistent grids (best
- * for a kernel running alone), n > 0 = short-lived CTAs of n iterations each.
+ * of neighbouring chunks.  codec_iterations_per_cta: n > 0 = short-lived CTAs
+ * of n iterations each for the encode / decode kernels (default 2, also the
+ * fastest for a kernel running alone), 0 = persistent grids.
  * collective_ctas: 0 = the all-reduce kernels fill the machine, n > 0 = at most
  * n CTAs.  Process-wide. */
 int nntrain_gradient_configure(int codec_iterations_per_cta, int collective_ctas);

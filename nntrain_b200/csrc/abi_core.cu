@@ -24,7 +24,7 @@ thread_local cudaStream_t t_implicit_stream = nullptr;
 constexpr int kMaxDevices = 64;
 int g_sm_counts[kMaxDevices] = {};
 
-std::atomic<int> g_codec_iterations_per_cta{0};
+std::atomic<int> g_codec_iterations_per_cta{2};
 std::atomic<int> g_collective_ctas{0};
 std::atomic<int> g_collective_async{1};
 std::atomic<int> g_codec_ctas{0};
@@ -140,8 +140,8 @@ NNTRAIN_EXPORT int nntrain_cuda_set_device(int device) {
 
 // Launch shapes for overlapping the collective with the codec kernels of
 // neighbouring chunks (ABI minor 36; the reference has no counterpart: its
-// kernels use fixed grids).  codec_iterations_per_cta: 0 = persistent grids,
-// n > 0 = short-lived CTAs of n iterations each.  collective_ctas: 0 = fill the
+// kernels use fixed grids).  codec_iterations_per_cta: n > 0 = short-lived CTAs
+// of n iterations each (default 2), 0 = persistent grids.  collective_ctas: 0 = fill the
 // machine, n > 0 = at most n CTAs for the all-reduce kernels.
 NNTRAIN_EXPORT int nntrain_gradient_configure(int codec_iterations_per_cta, int collective_ctas) {
     if (codec_iterations_per_cta < 0 || collective_ctas < 0) return static_cast<int>(cudaErrorInvalidValue);

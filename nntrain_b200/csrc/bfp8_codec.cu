@@ -37,7 +37,8 @@ template <int kBlock, int kFlags>
 cudaError_t run_fast(const float* source, float* writeback, signed char* payload, float* scales,
                      long long length, double* squared_sum, int* finite_status, cudaStream_t stream) {
     const long long tiles = (length + kWarpTile - 1) / kWarpTile;
-    const int grid = grid_for((tiles + kWarpsPerCta - 1) / kWarpsPerCta, kCtasPerSm);
+    const int grid = codec_grid_for((tiles + kWarpsPerCta - 1) / kWarpsPerCta,
+                                    resident_ctas_per_sm<bfp8_encode_blocks_kernel<kBlock, kFlags>>());
     bfp8_encode_blocks_kernel<kBlock, kFlags><<<grid, kThreads, 0, stream>>>(
         source, writeback, payload, scales, length, squared_sum, finite_status);
     return cudaPeekAtLastError();
@@ -63,7 +64,8 @@ cudaError_t run_warp(const float* source, float* writeback, signed char* payload
                      long long length, long long block, double* squared_sum, int* finite_status,
                      cudaStream_t stream) {
     const long long count = (length + block - 1) / block;
-    const int grid = grid_for((count + kWarpsPerCta - 1) / kWarpsPerCta, kCtasPerSm);
+    const int grid = codec_grid_for((count + kWarpsPerCta - 1) / kWarpsPerCta,
+                                    resident_ctas_per_sm<bfp8_encode_warp_per_block_kernel<kFlags>>());
     bfp8_encode_warp_per_block_kernel<kFlags><<<grid, kThreads, 0, stream>>>(
         source, writeback, payload, scales, length, block, count, squared_sum, finite_status);
     return cudaPeekAtLastError();
@@ -167,7 +169,7 @@ cudaError_t launch_bfp8_decode(const signed char* payload, const float* scales, 
     if (block > length) block = length;
     const long long words = (length + 3) / 4;
     if (aligned_to(payload, 4) && aligned_to(destination, 16)) {
-        const int grid = grid_for((words + kThreads * kDecodeUnroll - 1) / (kThreads * kDecodeUnroll), kCtasPerSm);
+        const int grid = codec_grid_for((words + kThreads * kDecodeUnroll - 1) / (kThreads * kDecodeUnroll), kCtasPerSm);
         if (block == 32) bfp8_decode_blocks_kernel<5><<<grid, kThreads, 0, stream>>>(payload, scales, destination, length, block);
         else if (block == 64) bfp8_decode_blocks_kernel<6><<<grid, kThreads, 0, stream>>>(payload, scales, destination, length, block);
         else if (block == 128) bfp8_decode_blocks_kernel<7><<<grid, kThreads, 0, stream>>>(payload, scales, destination, length, block);

@@ -21,6 +21,9 @@
 namespace ngb {
 
 constexpr int kCtasPerSmDefault = 8;
+constexpr int kThreads = 256;
+constexpr int kWarpsPerCta = kThreads / 32;
+constexpr int kCtasPerSm = 8;
 
 // ---- ABI / status ---------------------------------------------------------
 // Same numbering as the reference's native layer
@@ -63,11 +66,10 @@ cudaStream_t& implicit_stream();
 int sm_count();
 
 // Launch shape policy (process-wide, set by nntrain_gradient_configure):
-//   codec_iterations_per_cta  0: persistent grids (enough CTAs to fill every
-//       SM, each looping over the whole input) - best for a kernel running
-//       alone.  n > 0: every CTA does n loop iterations and retires, so that a
-//       kernel on another stream (the collective) finds free SM slots while a
-//       codec kernel runs.
+//   codec_iterations_per_cta  n > 0 (default 2): every CTA of an encode /
+//       decode kernel does n loop iterations and retires; a kernel on another
+//       stream (the collective) then finds free SM slots while a codec kernel
+//       runs.  0: persistent grids (one resident wave looping over the input).
 //   codec_ctas  n > 0 (with codec_iterations_per_cta == 0): persistent codec
 //       grids of at most n CTAs, which bounds the share of HBM bandwidth and
 //       of SM slots a codec kernel takes while the collective runs.
@@ -85,21 +87,47 @@ void set_launch_policy(int codec_iterations_per_cta, int collective_ctas);
 void set_collective_async(int enabled);
 void set_codec_ctas(int ctas);
 
-// Grid for `work_items` CTA-sized loop iterations: persistent (fill every SM
-// `per_sm` times, never more than the work needs) or, under the policy above,
-// one CTA per few iterations.
+// Persistent grid for `work_items` CTA-sized loop iterations: fill every SM
+// `per_sm` times, never more than the work needs.
 inline int grid_for(long long work_items, int per_sm) {
     if (work_items < 1) work_items = 1;
-    const int iterations = launch_policy().codec_iterations_per_cta;
-    if (iterations > 0) {
-        const long long ctas = (work_items + iterations - 1) / iterations;
+    long long cap = static_cast<long long>(sm_count()) * per_sm;
+    return static_cast<int>(work_items < cap ? work_items : cap);
+}
+
+// Grid for the encode / decode kernels under the launch policy: short-lived
+// CTAs of a few iterations each (the default, and the fastest measured: the
+// CTAs drift apart, which mixes DRAM reads and writes better than one resident
+// wave marching in step), or a persistent grid, optionally capped.
+inline int codec_grid_for(long long work_items, int per_sm) {
+    if (work_items < 1) work_items = 1;
+    const LaunchPolicy policy = launch_policy();
+    if (policy.codec_iterations_per_cta > 0) {
+        const long long ctas = (work_items + policy.codec_iterations_per_cta - 1) / policy.codec_iterations_per_cta;
         return static_cast<int>(ctas < 2147483647ll ? ctas : 2147483647ll);
     }
     long long cap = static_cast<long long>(sm_count()) * per_sm;
-    const int limit = launch_policy().codec_ctas;
-    if (limit > 0 && limit < cap) cap = limit;
+    if (policy.codec_ctas > 0 && policy.codec_ctas < cap) cap = policy.codec_ctas;
     return static_cast<int>(work_items < cap ? work_items : cap);
 }
+
+// CTAs of `kKernel` (kThreads threads, no dynamic shared memory) that fit on
+// one SM.  A persistent grid must be exactly one resident wave: with more CTAs
+// than fit, the surplus runs as a second, partly empty wave (a 48-register
+// kernel fits 5 CTAs per SM, so a grid of 8 per SM ran at 80 % of its speed).
+#ifdef __CUDACC__
+template <auto kKernel>
+int resident_ctas_per_sm() {
+    static int cached = 0;
+    if (cached == 0) {
+        int fit = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&fit, kKernel, kThreads, 0) != cudaSuccess || fit < 1)
+            fit = 4;
+        cached = fit;
+    }
+    return cached;
+}
+#endif
 
 // Grid for the all-reduce kernels.
 inline int collective_grid_for(long long work_items) {
@@ -109,9 +137,6 @@ inline int collective_grid_for(long long work_items) {
     return static_cast<int>(work_items < cap ? work_items : cap);
 }
 
-constexpr int kThreads = 256;
-constexpr int kWarpsPerCta = kThreads / 32;
-constexpr int kCtasPerSm = 8;
 
 // ---- device helpers -------------------------------------------------------
 #ifdef __CUDACC__

@@ -271,7 +271,7 @@ class Bfp8ArenaAllReduce:
             # high-priority stream, so the three stages share the SMs.
             overlapped = world > 1 and len(self.spans) > 1
             if codec_iterations_per_cta is None:
-                codec_iterations_per_cta = 4 if overlapped else 0
+                codec_iterations_per_cta = 2
             if collective_ctas is None:
                 # (with the copy-engine transport the owner kernel is local and short: no cap)
                 capped = overlapped and mode == PEER

@@ -243,7 +243,7 @@ def run_reference_arm(args, rank: int, world: int):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def time_kernels(args):
@@ -311,9 +311,9 @@ def time_kernels(args):
         torch.cuda.synchronize()
         ms = begin.elapsed_time(end) / runs
         achieved = nbytes / (ms * 1e-3) / 1e9
-        print(json.dumps({"kernel": name, "elements": E, "ms": round(ms, 4), "algorithmic_bytes": nbytes,
-                          "achieved_gbs": round(achieved, 1), "peak_gbs": peak, "peak_kind": kind,
-                          "frac": round(achieved / peak, 4)}), flush=True)
+        emit({"kernel": name, "elements": E, "ms": round(ms, 4), "algorithmic_bytes": nbytes,
+              "achieved_gbs": round(achieved, 1), "peak_gbs": peak, "peak_kind": kind,
+              "frac": round(achieved / peak, 4)})
 
 
 def time_phases(args, step, arena, world, rank, local_rank, barrier):
@@ -366,13 +366,37 @@ def time_phases(args, step, arena, world, rank, local_rank, barrier):
     wire = 2 * (world - 1) / world * (E + 4 * step.scale_count)
     out["allreduce_busbw_gbs"] = round(wire / (out["allreduce_ms"] * 1e-3) / 1e9, 1) if world > 1 else 0.0
     if rank == 0:
-        print(json.dumps({"phases": out, "n_gpus": world, "elements_per_rank": E, "transport": args.mode,
+        emit({"phases": out, "n_gpus": world, "elements_per_rank": E, "transport": args.mode,
                           "collective_ctas": step.collective_ctas,
-                          "codec_iterations_per_cta": step.codec_iterations_per_cta}), flush=True)
+              "codec_iterations_per_cta": step.codec_iterations_per_cta})
+
+
+_REAL_STDOUT = None
+
+
+def protect_stdout():
+    """Libraries loaded below (NCCL prints its version) may write to fd 1; the
+    contract is ONE JSON line on stdout, so everything else goes to stderr and
+    the line is written to the saved descriptor."""
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    text = (json.dumps(line) + "\n").encode()
+    if _REAL_STDOUT is None:
+        sys.stdout.write(text.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_REAL_STDOUT, text)
 
 
 def main():
     args = parse_args()
+    protect_stdout()
     if args.kernels:
         time_kernels(args)
         return
@@ -558,7 +582,7 @@ def main():
             "clocks": clocks,
             "result": {"norm": result.norm, "clip_coefficient": result.coefficient, "finite": result.finite},
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     step.close()
     group.close()
     if world > 1:

@@ -13,6 +13,7 @@ import re
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIBRARY_PATH = os.path.join(_HERE, "libnntrain_grad_b200.so")
 HEADER_PATH = os.path.join(_HERE, "..", "include", "nntrain_grad_abi.h")
+HEADER_PATHS = (HEADER_PATH, os.path.join(_HERE, "..", "include", "nntrain_host_plan.h"))
 
 
 class LibraryMissingError(ImportError):
@@ -61,8 +62,13 @@ def _ctype(decl: str):
     raise ValueError(f"cannot map C declaration {decl!r}")
 
 
-def declared_functions(header_path: str = HEADER_PATH) -> dict[str, tuple]:
-    """{name: (restype, [argtypes])} for every function the header declares."""
+def declared_functions(header_path: str | None = None) -> dict[str, tuple]:
+    """{name: (restype, [argtypes])} for every function the headers declare."""
+    if header_path is None:
+        merged = {}
+        for path in HEADER_PATHS:
+            merged.update(declared_functions(path))
+        return merged
     text = open(header_path).read()
     text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
     text = re.sub(r"^\s*#.*$", " ", text, flags=re.M)

@@ -75,7 +75,8 @@ def test_failed_calls_land_in_the_error_ring(lib):
 
 def test_every_declaration_carries_a_comment_and_the_header_cites_the_reference():
     import re
-    text = open(os.path.join(os.path.dirname(builder.__file__), "..", "include", "nntrain_grad_abi.h")).read()
+    include = os.path.join(os.path.dirname(builder.__file__), "..", "include")
+    text = open(os.path.join(include, "nntrain_grad_abi.h")).read() + open(os.path.join(include, "nntrain_host_plan.h")).read()
     for name in declared_functions():
         before = text[:text.index(name + "(")]
         last_statement = max(before.rfind(";"), before.rfind("{"))

@@ -1,0 +1,210 @@
+"""Host-side reducer bookkeeping (no GPU): bucket layout, the exactly-once
+publication state machine, step lifecycle, reduction stamps and the optimizer
+guard, following the reference's own host-logic tests."""
+import pytest
+
+from nntrain_b200.host_plan import (REDUCED, ArgumentError, CapturedGradientPublicationState, GradientStepPlan,
+                                    InvalidOperationError, build_buckets)
+
+
+def decoder_tensor_list():
+    # the 41.6 M-value decoder of benchmark configuration 1: token embedding,
+    # 8 layers of {qkv, out, ln, ffn in, ffn out, ln}, final ln
+    layer = [512 * 1536, 1536, 512 * 512, 512, 512, 512, 512 * 2048, 2048, 2048 * 512, 512, 512, 512]
+    return [32000 * 512] + layer * 8 + [512, 512]
+
+
+def test_bucket_layout_never_splits_a_tensor():
+    # NNtrain.Core/Training/CudaBFloat16GradientAllReduce.cs:1647-1678
+    numels = decoder_tensor_list()
+    assert sum(numels) == 41_604_096
+    placement, count = build_buckets(numels, 4 << 20)
+    sizes = [0] * count
+    for n, (bucket, offset) in zip(numels, placement):
+        assert offset == sizes[bucket]          # running sum, no padding
+        sizes[bucket] += n
+    assert sizes == [16_384_000, 3_940_352, 3_416_064, 3_152_384, 3_152_384, 3_152_384, 3_152_384, 3_152_384,
+                     2_101_760]
+    assert [b for b, _ in placement] == sorted(b for b, _ in placement)
+    placement, count = build_buckets([10, 20, 30], 25)       # 10+20 > 25: [10], [20], [30]
+    assert count == 3 and [p[0] for p in placement] == [0, 1, 2]
+    placement, count = build_buckets([10, 15, 1, 1], 25)      # closes exactly at the target
+    assert count == 2 and placement == [(0, 0), (0, 10), (1, 0), (1, 1)]
+    with pytest.raises(ArgumentError):
+        build_buckets([4, 0], 8)
+
+
+def test_captured_publication_requires_begun_current_step_and_is_exactly_once():
+    # NNtrain.Core.Tests/CudaCapturedGradientPublicationStateTests.cs:6-36
+    state = CapturedGradientPublicationState(2)
+    state.begin_step(17)
+    with pytest.raises(InvalidOperationError):
+        state.begin_captured_publication(17, 0, 3)
+    state.mark_device_begun(17, 0, 3)
+    state.mark_device_begun(17, 1, 7)
+    with pytest.raises(InvalidOperationError):
+        state.begin_captured_publication(16, 0, 3)
+    with pytest.raises(InvalidOperationError):
+        state.begin_captured_publication(18, 0, 3)
+    state.begin_captured_publication(17, 0, 3)
+    state.complete_captured_publication(17, 0, 3)
+    with pytest.raises(InvalidOperationError, match="twice"):
+        state.begin_captured_publication(17, 0, 3)
+    with pytest.raises(InvalidOperationError, match="mix"):
+        state.enter_notification_path(17, 1, 7)
+    state.begin_captured_publication(17, 1, 7)
+    state.complete_captured_publication(17, 1, 7)
+    state.validate_complete(17)
+    state.end_step(17)
+
+
+def test_capture_recording_suppresses_other_paths_and_must_be_discarded():
+    # NNtrain.Core.Tests/CudaCapturedGradientPublicationStateTests.cs:38-67
+    state = CapturedGradientPublicationState(2)
+    state.begin_step(23)
+    state.mark_device_begun(23, 0, 0)
+    state.mark_device_begun(23, 1, 1)
+    state.begin_capture_recording(23, 0, 0)
+    assert state.is_capture_recording(23, 0)
+    state.enter_capture_notification_path(23, 0, 0)
+    for forbidden in (lambda: state.enter_notification_path(23, 1, 1),
+                      lambda: state.begin_captured_publication(23, 1, 1),
+                      lambda: state.validate_complete(23),
+                      lambda: state.validate_capture_discard(23)):
+        with pytest.raises(InvalidOperationError):
+            forbidden()
+    state.end_capture_recording(23, 0, 0)
+    state.validate_capture_discard(23)
+    state.end_step(23)
+    state.begin_step(24)
+    state.mark_device_begun(24, 0, 0)
+    state.enter_notification_path(24, 0, 0)
+    state.validate_complete(24)
+    state.end_step(24)
+
+
+def test_mid_publication_failure_requires_abort_generation_before_reuse():
+    # NNtrain.Core.Tests/CudaCapturedGradientPublicationStateTests.cs:69-95
+    state = CapturedGradientPublicationState(2)
+    state.begin_step(31)
+    state.mark_device_begun(31, 0, 0)
+    state.mark_device_begun(31, 1, 1)
+    state.begin_captured_publication(31, 0, 0)
+    state.fail_captured_publication(31, 0)
+    with pytest.raises(InvalidOperationError):
+        state.begin_captured_publication(31, 1, 1)
+    with pytest.raises(InvalidOperationError):
+        state.validate_complete(31)
+    state.end_step(31)
+    state.begin_step(32)
+    for slot in (0, 1):
+        state.mark_device_begun(32, slot, slot)
+    for slot in (0, 1):
+        state.begin_captured_publication(32, slot, slot)
+        state.complete_captured_publication(32, slot, slot)
+    state.validate_complete(32)
+    state.end_step(32)
+    with pytest.raises(InvalidOperationError):
+        state.begin_step(33) or state.begin_step(34)      # a second begin while active
+
+
+def reduce_once(plan: GradientStepPlan, order=None) -> list[int]:
+    """Runs one whole step; returns the order buckets were enqueued in."""
+    step = plan.begin_step()
+    plan.begin_device_step(step)
+    tensors = list(range(len(decoder_tensor_list()))) if order is None else order
+    enqueued = []
+    for tensor in tensors:
+        plan.notify_gradient_ready(tensor, step)
+        while (bucket := plan.next_enqueueable(step)) >= 0:
+            enqueued.append(bucket)
+    plan.complete(step)
+    return enqueued
+
+
+def test_step_lifecycle_duplicate_notification_abort_and_recover():
+    # NNtrain.Core.Tests/CudaGradientCoherenceTests.cs:74-113,
+    # CudaBfp8GradientReducerTests.cs:59-93
+    plan = GradientStepPlan(decoder_tensor_list(), devices=[0, 1])
+    assert plan.bucket_count == 9
+    failed = plan.begin_step()
+    with pytest.raises(InvalidOperationError, match="still active"):
+        plan.begin_step()
+    with pytest.raises(InvalidOperationError, match="not begun"):
+        plan.notify_gradient_ready(0, failed)
+    plan.begin_device_step(failed)
+    with pytest.raises(InvalidOperationError, match="twice"):
+        plan.begin_device_step(failed)
+    plan.notify_gradient_ready(5, failed)
+    with pytest.raises(InvalidOperationError, match="notified twice"):
+        plan.notify_gradient_ready(5, failed)
+    with pytest.raises(InvalidOperationError, match="not completed"):
+        plan.complete(failed)                       # buckets still outstanding
+    assert plan.coherence_snapshot(5)["pending_step"] == failed
+    plan.abort(failed)
+    assert plan.coherence_snapshot(5)["pending_step"] == 0
+    with pytest.raises(InvalidOperationError, match="not active"):
+        plan.notify_gradient_ready(6, failed)
+    order = reduce_once(plan)
+    assert order == list(range(8, -1, -1))          # fixed order, descending bucket index
+    snapshot = plan.coherence_snapshot(5)
+    assert snapshot["kind"] == REDUCED and snapshot["stamp"][1] == 2 and plan.completed_steps == 1
+    plan.close()
+
+
+def test_non_finite_step_fails_complete_and_stays_abortable():
+    # NNtrain.Core.Tests/CudaBfp8GradientReducerTests.cs:95-130
+    plan = GradientStepPlan([100, 200], devices=[0, 1], target_bucket_elements=1000)
+    step = plan.begin_step()
+    plan.begin_device_step(step)
+    for tensor in (1, 0):
+        plan.notify_gradient_ready(tensor, step)
+    assert plan.next_enqueueable(step) == 0
+    with pytest.raises(InvalidOperationError, match="non-finite"):
+        plan.complete(step, non_finite=True)
+    plan.abort(step)
+    with pytest.raises(InvalidOperationError, match="has not been reduced"):
+        plan.optimizer_validate_and_consume()
+    plan.close()
+
+
+def test_optimizer_guard_is_fail_closed():
+    # NNtrain.Core.Tests/CudaGradientCoherenceTests.cs:6-72,115-150;
+    # NNtrain.Core/Training/CudaGradientCoherence.cs:61-173
+    plan = GradientStepPlan([64, 64, 64], devices=[0, 1], target_bucket_elements=100)
+    with pytest.raises(InvalidOperationError, match="already consumed|has not been reduced"):
+        plan.optimizer_validate_and_consume()               # nothing was ever produced
+    step = plan.begin_step()
+    with pytest.raises(InvalidOperationError, match="incomplete reduction step"):
+        plan.optimizer_validate_and_consume()
+    plan.abort(step)
+    reduce_once(plan, order=[2, 1, 0])
+    with pytest.raises(InvalidOperationError, match="has not been reduced"):
+        plan.optimizer_validate_and_consume([0, 2])          # another device set
+    with pytest.raises(InvalidOperationError, match="unique"):
+        plan.optimizer_validate_and_consume([0, 0])
+    plan.optimizer_validate_and_consume()
+    with pytest.raises(InvalidOperationError, match="already consumed"):
+        plan.optimizer_validate_and_consume()                # the same gradients twice
+    reduce_once(plan, order=[0, 1, 2])
+    plan.optimizer_validate_and_consume()
+    # a rebuilt reducer invalidates the old, unconsumed stamp
+    reduce_once(plan, order=[0, 1, 2])
+    rebuilt = GradientStepPlan([64, 64, 64], devices=[0, 1], target_bucket_elements=100)
+    with pytest.raises(InvalidOperationError, match="has not been reduced"):
+        plan.optimizer_validate_and_consume()
+    rebuilt.close()
+    plan.close()
+
+
+def test_transport_bytes_formula():
+    # 2 devices, block 128: 2 * (E + 4 * ceil(E / 128)) per pair, i.e. half per
+    # rank (NNtrain.Core.Tests/CudaMix8GradientTransportTests.cs:267-270)
+    numels = [515, 300, 1000]
+    plan = GradientStepPlan(numels, devices=[0, 1], target_bucket_elements=1 << 20, block_size=128)
+    e = sum(numels)
+    assert plan.transport_bytes_per_step == (e + 4 * ((e + 127) // 128))
+    plan.close()
+    plan = GradientStepPlan(numels, devices=list(range(8)), target_bucket_elements=1 << 20, block_size=32)
+    assert plan.transport_bytes_per_step == 2 * 7 * (e + 4 * ((e + 31) // 32)) // 8
+    plan.close()

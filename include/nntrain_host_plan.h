@@ -103,6 +103,14 @@ int nntrain_plan_coherence_snapshot(void* plan, int tensor, long long* out6);
 /* CudaGradientOptimizerGuard.ValidateAndConsume, CudaGradientCoherence.cs:61-173 */
 int nntrain_plan_optimizer_validate_and_consume(void* plan, const int* devices, int device_count);
 
+/* PublishGradientSquaredSum, NNtrain.Core/Tensors/Tensor.CudaKernels.cs:768-798 */
+int nntrain_plan_publish_squared_sum(void* plan, const int* devices, int device_count, double squared_sum);
+/* TryConsumeGradientSquaredSum, Tensor.CudaKernels.cs:800-829,831-848 */
+int nntrain_plan_try_consume_squared_sum(void* plan, const int* devices, int device_count,
+                                         double* squared_sum, int* hit);
+/* clip decision of clip_grad_norm_, NNtrain.Core/Torch/nn.cs:41-47,69-72 */
+int nntrain_gradient_clip_decision(double squared_sum, float max_norm, float* norm, float* coefficient);
+
 #ifdef __cplusplus
 }
 #endif

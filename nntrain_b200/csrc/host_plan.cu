@@ -141,6 +141,12 @@ struct StepPlan {
     long long device_begun_step = 0;
     long long completed_steps = 0;
     int next_in_order = 0;                 // buckets are enqueued in descending index order
+    // one-shot cache of the step's fused sum of squares, valid for exactly the
+    // gradient versions it was published with
+    bool cache_valid = false;
+    double cache_value = 0.0;
+    std::vector<long long> cache_versions;
+    std::vector<int> cache_devices;
     std::mutex mutex;
 };
 
@@ -638,5 +644,58 @@ NNTRAIN_EXPORT int nntrain_plan_optimizer_validate_and_consume(void* plan, const
         r.consumed_version = r.version;
         if (device_count > 1) r.consumed_stamp = expected;
     }
+    return kOk;
+}
+
+// ---- fused sum-of-squares cache and the clip decision ------------------------------------
+// The reducer publishes the sum of squares it fused into the reduction; the
+// clip consumes it once, and only if no gradient changed since
+// (NNtrain.Core/Tensors/Tensor.CudaKernels.cs:768-854).  A non-finite or
+// negative value is not cached.
+NNTRAIN_EXPORT int nntrain_plan_publish_squared_sum(void* plan, const int* devices, int device_count,
+                                                    double squared_sum) {
+    auto* p = static_cast<StepPlan*>(plan);
+    if (!p || !devices || device_count <= 0) return fail(kBadArgument, "null argument.");
+    if (!std::isfinite(squared_sum) || squared_sum < 0.0) return kOk;
+    std::lock_guard<std::mutex> guard(p->mutex);
+    p->cache_versions.clear();
+    for (const GradientRecord& r : p->records) p->cache_versions.push_back(r.version);
+    p->cache_devices.assign(devices, devices + device_count);
+    p->cache_value = squared_sum;
+    p->cache_valid = true;
+    return kOk;
+}
+
+// *hit = 1 and *squared_sum = the cached value when the cache matches the
+// device set and every gradient version; the entry is dropped either way.
+NNTRAIN_EXPORT int nntrain_plan_try_consume_squared_sum(void* plan, const int* devices, int device_count,
+                                                        double* squared_sum, int* hit) {
+    auto* p = static_cast<StepPlan*>(plan);
+    if (!p || !devices || device_count <= 0 || !squared_sum || !hit) return fail(kBadArgument, "null argument.");
+    std::lock_guard<std::mutex> guard(p->mutex);
+    *hit = 0;
+    *squared_sum = 0.0;
+    if (!p->cache_valid) return kOk;
+    p->cache_valid = false;
+    if (static_cast<int>(p->cache_devices.size()) != device_count) return kOk;
+    for (int d = 0; d < device_count; ++d)
+        if (p->cache_devices[d] != devices[d]) return kOk;
+    for (size_t i = 0; i < p->records.size(); ++i)
+        if (p->records[i].version != p->cache_versions[i]) return kOk;
+    *hit = 1;
+    *squared_sum = p->cache_value;
+    return kOk;
+}
+
+// norm = (float)sqrt(squared_sum); coefficient = norm > max_norm ?
+// max_norm / (norm + 1e-6f) : 1 (NNtrain.Core/Torch/nn.cs:69-72).  max_norm
+// must be positive (nn.cs:41-47).
+NNTRAIN_EXPORT int nntrain_gradient_clip_decision(double squared_sum, float max_norm, float* norm,
+                                                  float* coefficient) {
+    if (!norm || !coefficient) return fail(kBadArgument, "null argument.");
+    if (!(max_norm > 0.0f)) return fail(kBadArgument, "The maximum gradient norm must be positive.");
+    const float total = static_cast<float>(std::sqrt(squared_sum));
+    *norm = total;
+    *coefficient = total > max_norm ? max_norm / (total + 1e-6f) : 1.0f;
     return kOk;
 }

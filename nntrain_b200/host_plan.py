@@ -166,3 +166,25 @@ class GradientStepPlan:
         devices = self.devices if devices is None else list(devices)
         _check(load().nntrain_plan_optimizer_validate_and_consume(
             self._handle, (ctypes.c_int * max(1, len(devices)))(*devices), len(devices)))
+
+    def publish_squared_sum(self, squared_sum: float, devices=None) -> None:
+        devices = self.devices if devices is None else list(devices)
+        _check(load().nntrain_plan_publish_squared_sum(
+            self._handle, (ctypes.c_int * len(devices))(*devices), len(devices), squared_sum))
+
+    def try_consume_squared_sum(self, devices=None):
+        """The cached fused sum of squares, or None on a miss (one shot)."""
+        devices = self.devices if devices is None else list(devices)
+        value, hit = ctypes.c_double(), ctypes.c_int()
+        _check(load().nntrain_plan_try_consume_squared_sum(
+            self._handle, (ctypes.c_int * len(devices))(*devices), len(devices), ctypes.addressof(value),
+            ctypes.addressof(hit)))
+        return value.value if hit.value else None
+
+
+def clip_decision(squared_sum: float, max_norm: float) -> tuple[float, float]:
+    """(pre-clip norm, coefficient) of clip_grad_norm_ (NNtrain.Core/Torch/nn.cs:32-81)."""
+    norm, coefficient = ctypes.c_float(), ctypes.c_float()
+    _check(load().nntrain_gradient_clip_decision(squared_sum, max_norm, ctypes.addressof(norm),
+                                                 ctypes.addressof(coefficient)))
+    return norm.value, coefficient.value

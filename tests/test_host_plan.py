@@ -4,7 +4,7 @@ guard, following the reference's own host-logic tests."""
 import pytest
 
 from nntrain_b200.host_plan import (REDUCED, ArgumentError, CapturedGradientPublicationState, GradientStepPlan,
-                                    InvalidOperationError, build_buckets)
+                                    InvalidOperationError, build_buckets, clip_decision)
 
 
 def decoder_tensor_list():
@@ -208,3 +208,30 @@ def test_transport_bytes_formula():
     plan = GradientStepPlan(numels, devices=list(range(8)), target_bucket_elements=1 << 20, block_size=32)
     assert plan.transport_bytes_per_step == 2 * 7 * (e + 4 * ((e + 31) // 32)) // 8
     plan.close()
+
+
+def test_fused_squared_sum_cache_is_one_shot_and_version_checked(oracle):
+    # NNtrain.Core/Tensors/Tensor.CudaKernels.cs:768-854;
+    # NNtrain.Core.Tests/CudaBfp8GradientClipNormTests.cs:192-200 (a hit costs no kernel)
+    plan = GradientStepPlan([64, 64], devices=[0, 1], target_bucket_elements=1000)
+    assert plan.try_consume_squared_sum() is None
+    reduce_once(plan, order=[1, 0])
+    plan.publish_squared_sum(12.5)
+    assert plan.try_consume_squared_sum([0, 2]) is None      # other device set: miss, and the entry is gone
+    assert plan.try_consume_squared_sum() is None
+    plan.publish_squared_sum(12.5)
+    assert plan.try_consume_squared_sum() == 12.5
+    assert plan.try_consume_squared_sum() is None            # one shot
+    plan.publish_squared_sum(float("nan"))                    # never cached
+    assert plan.try_consume_squared_sum() is None
+    plan.publish_squared_sum(3.0)
+    reduce_once(plan, order=[0, 1])                           # gradients changed since
+    assert plan.try_consume_squared_sum() is None
+    plan.close()
+    # the clip decision itself, against the oracle's restatement of nn.cs:62-81
+    for squared_sum, max_norm in ((1e-6, 1.0), (4.0, 1.0), (1066.2 ** 2, 1.0), (0.0, 0.5)):
+        norm, c = clip_decision(squared_sum, max_norm)
+        expect_norm, expect_c = oracle.clip_coefficient(squared_sum, max_norm)
+        assert norm == expect_norm and c == expect_c
+    with pytest.raises(ArgumentError):
+        clip_decision(1.0, 0.0)

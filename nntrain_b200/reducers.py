@@ -436,6 +436,78 @@ class Bfp8ArenaAllReduce:
         self.scales_buffer.close()
 
 
+class Bf16ArenaAllReduce:
+    """All-reduce of a bf16 gradient arena across the group: fp32 accumulate in
+    rank order, bf16 (round to nearest even) result in place on every rank, sum
+    of squares of the bf16 result, then the clip `g = bf16(f32(g) * c)`.
+
+    The arena-mode reducer of the reference
+    (`CudaBFloat16GradientAllReducePlan` with bf16 gradient storage,
+    NNtrain.Core/Training/CudaBFloat16GradientAllReduce.cs:538-541,1413-1459;
+    clip: NNtrain.Core/Tensors/Tensor.CudaKernels.cs:176-319) for N ranks.
+    `values` is this rank's arena (bf16 bit patterns as int16) in peer-visible
+    memory: backward accumulates straight into it, nothing is packed."""
+
+    def __init__(self, group: GradientGroup, elements: int, mode: int = PEER, reduction_scale: float = 1.0,
+                 chunk_elements: int | None = None):
+        self.group, self.elements, self.mode, self.reduction_scale = group, elements, mode, reduction_scale
+        world, device = group.world, group.device
+        align = 512 * world
+        if chunk_elements is None or chunk_elements >= elements:
+            chunk_elements = elements
+        else:
+            chunk_elements = max(align, chunk_elements // align * align)
+        self.spans = [(a, min(a + chunk_elements, elements)) for a in range(0, elements, chunk_elements)]
+        with torch.cuda.device(device):
+            self.buffer = PeerBuffer(group, elements * 2)
+            self.values = self.buffer.tensor(torch.int16, elements)
+            self.squared_sum = torch.zeros(1, dtype=torch.float64, device=f"cuda:{device}")
+            self.staging = None
+            if mode != PEER and world > 1:
+                first, end = shard_range(chunk_elements, world, 0)
+                shard = (end - first + 511) // 512 * 512
+                self.staging = torch.empty(world * shard, dtype=torch.int16, device=f"cuda:{device}")
+        check("gradient_configure", load().nntrain_gradient_configure(2, 0))
+
+    @property
+    def transport_bytes_per_step(self) -> int:
+        """2 (N-1)/N * 2 E; for N = 2 the reference's 2 * 2 * E per pair
+        (NNtrain.Core/Training/CudaBFloat16GradientAllReduce.cs:292-297)."""
+        world = self.group.world
+        return 2 * (world - 1) * 2 * self.elements // world
+
+    def enqueue(self) -> None:
+        device, lib = self.group.device, load()
+        stream = torch.cuda.current_stream(device)
+        self.squared_sum.zero_()
+        for index, (start, stop) in enumerate(self.spans):
+            table = _pointer_table([p + 2 * start for p in self.buffer.pointers])
+            phase = (1 if index == 0 else 0) | (2 if index == len(self.spans) - 1 else 0)
+            check("gradient_allreduce_bf16", lib.nntrain_gradient_allreduce_bf16(
+                self.group.handle, table, stop - start, self.reduction_scale, self.squared_sum.data_ptr(),
+                self.mode, phase, 0 if self.staging is None else self.staging.data_ptr(), stream.cuda_stream))
+
+    def complete(self, max_norm: float | None = None) -> StepResult:
+        """Reads the sum of squares (8 bytes) and applies the clip."""
+        from .host_plan import clip_decision
+        device = self.group.device
+        torch.cuda.current_stream(device).synchronize()
+        squared_sum = float(self.squared_sum.item())
+        finite = squared_sum == squared_sum and squared_sum != float("inf")
+        if not finite:
+            raise FloatingPointError("BF16 gradient reduction saw a non-finite gradient")
+        norm, coefficient = clip_decision(squared_sum, max_norm if max_norm is not None else 3.0e38)
+        if max_norm is not None and coefficient != 1.0:
+            GradientNorm.clip_apply(device, GradientNorm.BF16, self.values, multiplier=coefficient)
+            torch.cuda.current_stream(device).synchronize()
+        return StepResult(norm, coefficient, squared_sum, finite)
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.group.device)
+        self.values = None
+        self.buffer.close()
+
+
 def smoke_check(oracle) -> None:
     """Two emulated ranks on one GPU: the owner kernel against the oracle."""
     import numpy as np

@@ -55,6 +55,28 @@ def main() -> None:
             if step.transport_bytes_per_step != expected_bytes:
                 failures.append(f"{tag}: transport bytes")
             step.close()
+    # bf16 arena reducer: fp32 accumulate in rank order, bf16 result, clip
+    for mode in (reducers.PEER, reducers.NCCL):
+        for n, chunk in ((515, None), ((1 << 20) + 1024, None), (1 << 20, 1 << 18)):
+            inputs = [oracle.bf16_encode(oracle.generate_gradient(n, 0xB2000002 + n, r, sigma_lo=1e-3, sigma_hi=1e-3,
+                                                                  outlier_fraction=0.0, zero_fraction=0.0,
+                                                                  subnormals=0), 1) for r in range(world)]
+            step = reducers.Bf16ArenaAllReduce(group, n, mode, reduction_scale=1.0, chunk_elements=chunk)
+            for _ in range(2):
+                step.values.copy_(torch.from_numpy(inputs[rank].view(np.int16)))
+                step.enqueue()
+                result = step.complete(max_norm=0.05)
+            _, expect_bf16, expect_sq = oracle.bf16_reduce(inputs, 1.0, want_bf16=True, square_of_bf16=True)
+            norm, c = oracle.clip_coefficient(expect_sq, 0.05)
+            expect = oracle.scale_bf16(expect_bf16, c) if c != 1.0 else expect_bf16
+            tag = f"bf16 mode={mode} n={n} chunk={chunk}"
+            if not np.array_equal(step.values.cpu().numpy().view(np.uint16), expect):
+                failures.append(f"{tag}: arena differs")
+            if abs(result.squared_sum - expect_sq) > 1e-9 * expect_sq or abs(result.coefficient - c) > 2e-6 * c:
+                failures.append(f"{tag}: sum of squares / coefficient")
+            if step.transport_bytes_per_step != 2 * (world - 1) * 2 * n // world:
+                failures.append(f"{tag}: transport bytes")
+            step.close()
     # a NaN on one rank fails the step on every rank
     n = 1 << 16
     g = oracle.generate_gradient(n, 7, rank)

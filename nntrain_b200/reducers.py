@@ -369,6 +369,9 @@ class Bfp8ArenaAllReduce:
                                                self.final_events[index - 1])
             if last:
                 launches += self._result_final(index, gradient, host_payload, self.write_fp32)
+        # The decodes read the scale sidecar as reduced; the clip rewrites it in
+        # place, so it must not start before the last decode has finished.
+        self.communication_stream.wait_stream(self.decode_stream)
         with torch.cuda.stream(self.communication_stream):
             if max_norm is not None:
                 GradientNorm.clip_coefficient(device, self.squared_sum, max_norm, self.norm_and_coefficient,

@@ -432,7 +432,7 @@ def main():
     step = reducers.Bfp8ArenaAllReduce(group, E, BLOCK, mode, chunk_elements=chunk or None,
                                        reduction_scale=1.0 / world, write_fp32=True, **shape)
     if args.codec_ctas:
-        load().nntrain_gradient_configure_collective(step.collective_async | (args.codec_ctas << 8))
+        load().nntrain_gradient_configure_codec_cap(args.codec_ctas)
     device_chunks = [b - a for a, b in step.spans]
     device_chunk, device_shape = step.chunk, (step.codec_iterations_per_cta, step.collective_ctas)
     arena = torch.empty(E, dtype=torch.float32, device=device)

@@ -74,10 +74,12 @@ int nntrain_cuda_use_external_stream(void* stream);
 int nntrain_gradient_configure(int codec_iterations_per_cta, int collective_ctas);
 /* ABI minor 36; no counterpart in the reference.  How the all-reduce kernels
  * fetch their inputs: 1 (default) = cp.async rings in shared memory, 0 =
- * register prefetch.  Same results either way.  Bits 8 and up, when non-zero:
- * the most CTAs a persistent codec grid may use (bounds the share of HBM
- * bandwidth a codec kernel takes while the collective runs). */
+ * register prefetch.  Same results either way. */
 int nntrain_gradient_configure_collective(int asynchronous_copies);
+/* ABI minor 36; no counterpart in the reference.  Most CTAs a persistent
+ * encode / decode grid may use (only with codec_iterations_per_cta == 0);
+ * 0 = no cap. */
+int nntrain_gradient_configure_codec_cap(int ctas);
 
 /* ---- BFP8 block codec ---------------------------------------------------
  * payload: signed int8 per value; scales: one fp32 per block,

@@ -151,11 +151,18 @@ NNTRAIN_EXPORT int nntrain_gradient_configure(int codec_iterations_per_cta, int 
 
 // Chooses how the all-reduce kernels fetch their inputs (ABI minor 36, no
 // counterpart in the reference): 1 (default) = cp.async rings in shared
-// memory, 0 = register prefetch.  Same results either way.  Bits 8 and up:
-// when non-zero, the cap on the CTAs of a persistent codec grid.
+// memory, 0 = register prefetch.  Same results either way.
 NNTRAIN_EXPORT int nntrain_gradient_configure_collective(int asynchronous_copies) {
-    set_collective_async(asynchronous_copies & 1);
-    set_codec_ctas(asynchronous_copies >> 8);
+    set_collective_async(asynchronous_copies != 0);
+    return static_cast<int>(cudaSuccess);
+}
+
+// Caps the CTAs of a persistent encode / decode grid (only used when
+// codec_iterations_per_cta is 0): bounds the share of HBM bandwidth and SM
+// slots a codec kernel takes while the collective runs.  0 = no cap.
+NNTRAIN_EXPORT int nntrain_gradient_configure_codec_cap(int ctas) {
+    if (ctas < 0) return static_cast<int>(cudaErrorInvalidValue);
+    set_codec_ctas(ctas);
     return static_cast<int>(cudaSuccess);
 }
 

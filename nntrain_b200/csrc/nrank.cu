@@ -152,9 +152,7 @@ __global__ void fold_flags_kernel(double* scratch, const int* finite_status) {
 }
 
 // After the sum over ranks: add the job-wide sum of squares, raise the flag.
-__global__ void publish_totals_kernel(const double* scratch, const int* shard_flag, double* squared_sum,
-                                      int* finite_status) {
-    (void)shard_flag;
+__global__ void publish_totals_kernel(const double* scratch, double* squared_sum, int* finite_status) {
     if (squared_sum != nullptr) *squared_sum += scratch[0];
     if (finite_status != nullptr && scratch[1] != 0.0) *finite_status = 1;
 }
@@ -570,7 +568,7 @@ NNTRAIN_EXPORT int nntrain_gradient_allreduce_bfp8(
     // Sum of the shards' partials over ranks; in peer mode this collective is
     // also the fence after which every rank's arena is complete.
     if (world > 1 && (status = sum_partials(g, stream)) != 0) return status;
-    publish_totals_kernel<<<1, 1, 0, stream>>>(g->scratch, shard_flag, squared_sum, finite_status);
+    publish_totals_kernel<<<1, 1, 0, stream>>>(g->scratch, squared_sum, finite_status);
     return static_cast<int>(cudaPeekAtLastError());
 }
 
@@ -649,7 +647,7 @@ NNTRAIN_EXPORT int nntrain_gradient_allreduce_bf16(
     }
     if (!(phase & kPhaseEnd)) return 0;
     if (world > 1 && (status = sum_partials(g, stream)) != 0) return status;
-    publish_totals_kernel<<<1, 1, 0, stream>>>(g->scratch, nullptr, squared_sum, nullptr);
+    publish_totals_kernel<<<1, 1, 0, stream>>>(g->scratch, squared_sum, nullptr);
     return static_cast<int>(cudaPeekAtLastError());
 }
 

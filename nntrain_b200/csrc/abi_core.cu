@@ -43,7 +43,12 @@ int complete(Operation operation, int device, int status) {
 }
 
 int select_device(int device) {
-    if (t_selected_device == device) return static_cast<int>(cudaSuccess);
+    // The cached selection is trusted only when the runtime agrees: another
+    // library in the process (the host's tensor library, a second gateway) may
+    // have switched the thread's device since the last call.
+    int current = -1;
+    if (t_selected_device == device && cudaGetDevice(&current) == cudaSuccess && current == device)
+        return static_cast<int>(cudaSuccess);
     cudaError_t status = cudaSetDevice(device);
     if (status == cudaSuccess) t_selected_device = device;
     return static_cast<int>(status);

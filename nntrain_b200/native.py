@@ -216,6 +216,37 @@ class CudaGradientBuckets:
             reduced.numel(), _ptr(squared_sum), communication_stream, local_ready, remote_ready))
 
     @staticmethod
+    def create_host_pipeline(source_device: int, destination_device: int, chunk_elements: int,
+                             bfp8_block: bool = False) -> int:
+        """The pinned-host fallback for a device pair without peer access."""
+        import ctypes
+        handle = ctypes.c_void_p()
+        fn = (load().nntrain_gradient_host_pipeline_create_bfp8_block if bfp8_block
+              else load().nntrain_gradient_host_pipeline_create)
+        check("gradient_host_pipeline_create", fn(source_device, destination_device, chunk_elements,
+                                                  ctypes.addressof(handle)))
+        return handle.value
+
+    @staticmethod
+    def host_pipeline_exchange(pipeline: int, local, remote_source, reduced, squared_sum, local_ready: int,
+                               remote_ready: int) -> None:
+        check("gradient_host_pipeline_exchange_bf16", load().nntrain_gradient_host_pipeline_exchange_bf16(
+            pipeline, _ptr(local), _ptr(remote_source), _ptr(reduced), reduced.numel(), _ptr(squared_sum),
+            local_ready, remote_ready))
+
+    @staticmethod
+    def host_pipeline_exchange_bfp8_block(pipeline: int, local, local_scales, remote_source, remote_source_scales,
+                                          reduced, squared_sum, local_ready: int, remote_ready: int) -> None:
+        check("gradient_host_pipeline_exchange_bfp8_block",
+              load().nntrain_gradient_host_pipeline_exchange_bfp8_block(
+                  pipeline, _ptr(local), _ptr(local_scales), _ptr(remote_source), _ptr(remote_source_scales),
+                  _ptr(reduced), reduced.numel(), _ptr(squared_sum), local_ready, remote_ready))
+
+    @staticmethod
+    def destroy_host_pipeline(pipeline: int) -> None:
+        check("gradient_host_pipeline_destroy", load().nntrain_gradient_host_pipeline_destroy(pipeline))
+
+    @staticmethod
     def unpack(device: int, source, source_offset: int, destination, communication_stream: int) -> None:
         check("gradient_unpack_float", load().nntrain_gradient_unpack_float(
             device, _ptr(source), source_offset, _ptr(destination), destination.numel(), communication_stream))

@@ -156,3 +156,44 @@ def test_bucket_exchanges_across_two_devices(two_devices, oracle, n):
     for d in (0, 1):
         CudaGradientBuckets.destroy_event(d, events[d])
         CudaGradientBuckets.destroy_communication_stream(d, streams[d])
+
+
+def test_pinned_host_pipeline_gives_the_same_sums(two_devices, oracle):
+    # the no-peer-access fallback: chunks bounce through pinned host memory,
+    # double-buffered; results must equal the peer-copy exchange
+    # (NNtrain.Cuda/native/gradient_collectives.cu:359-709;
+    #  NNtrain.Core.Tests/CudaMix8GradientTransportTests.cs:108-219)
+    chunk = 4096
+    n = 3 * chunk + 515                       # three full chunks and a ragged one
+    g = [vectors.config0_gradient(oracle, r, n) for r in (0, 1)]
+    packed = [oracle.pack_bfp8_block(x, 128) for x in g]
+    bf16 = [oracle.bf16_encode(x, 1) for x in g]
+    expect_block, expect_block_sq = oracle.block_transport_sum([p[0] for p in packed], [p[1] for p in packed], 128)
+    expect_bf16, _, expect_bf16_sq = oracle.bf16_reduce(bf16)
+    local_p, local_s, local_16 = on(0, packed[0][0]), on(0, packed[0][1]), on(0, bf16[0].view(np.int16))
+    remote_p, remote_s, remote_16 = on(1, packed[1][0]), on(1, packed[1][1]), on(1, bf16[1].view(np.int16))
+    events = []
+    for d in (0, 1):
+        with torch.cuda.device(d):
+            torch.cuda.synchronize(d)
+            event = CudaGradientBuckets.create_ready_event(d)
+            CudaGradientBuckets.record_ready(d, event)
+            events.append(event)
+    reduced = torch.zeros(n, dtype=torch.float32, device="cuda:0")
+    sq = torch.zeros(1, dtype=torch.float64, device="cuda:0")
+    pipeline = CudaGradientBuckets.create_host_pipeline(1, 0, chunk, bfp8_block=True)
+    CudaGradientBuckets.host_pipeline_exchange_bfp8_block(pipeline, local_p, local_s, remote_p, remote_s, reduced, sq,
+                                                          events[0], events[1])
+    CudaGradientBuckets.destroy_host_pipeline(pipeline)
+    assert_bits_equal(host(reduced), expect_block, "block transport through the host pipeline")
+    assert sq.item() == pytest.approx(expect_block_sq, rel=1e-12)
+    reduced.zero_()
+    sq.zero_()
+    torch.cuda.synchronize(0)
+    pipeline = CudaGradientBuckets.create_host_pipeline(1, 0, chunk)
+    CudaGradientBuckets.host_pipeline_exchange(pipeline, local_16, remote_16, reduced, sq, events[0], events[1])
+    CudaGradientBuckets.destroy_host_pipeline(pipeline)
+    assert_bits_equal(host(reduced), expect_bf16, "bf16 transport through the host pipeline")
+    assert sq.item() == pytest.approx(expect_bf16_sq, rel=1e-12)
+    for d in (0, 1):
+        CudaGradientBuckets.destroy_event(d, events[d])

@@ -27,9 +27,9 @@ def test_all_reduce_across_processes(cuda, world):
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
          "--master-addr", "127.0.0.1", "--master-port", str(free_port()), worker],
         capture_output=True, text=True, timeout=600, env=env)
-    # keep the ranks' output where a remote run brings it back
-    log_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
-    if os.path.isdir(log_dir):
+    # keep the ranks' output when a log directory is given
+    log_dir = os.environ.get("NNTRAIN_TEST_LOG_DIR", "")
+    if log_dir and os.path.isdir(log_dir):
         with open(os.path.join(log_dir, f"multi_gpu_worker_{world}.log"), "w") as log:
             log.write(done.stdout + "\n--- stderr ---\n" + done.stderr)
     relevant = "\n".join(line for line in (done.stdout + done.stderr).splitlines()

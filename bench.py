@@ -509,9 +509,9 @@ def main():
     # -- end to end: pinned host buffers in, encoded result out -----------------------------
     e2e = None
     if not args.no_e2e:
-        host_gradient = torch.empty(E, dtype=torch.float32).pin_memory()
-        host_payload = torch.empty(E, dtype=torch.int8).pin_memory()
-        host_scales = torch.empty(step.scale_count, dtype=torch.float32).pin_memory()
+        host_gradient = torch.empty(E, dtype=torch.float32, pin_memory=True)
+        host_payload = torch.empty(E, dtype=torch.int8, pin_memory=True)
+        host_scales = torch.empty(step.scale_count, dtype=torch.float32, pin_memory=True)
         host_gradient.copy_(arena)
         e2e_chunk = 64 << 20
         e2e_step = step if (step.chunk <= e2e_chunk) else None

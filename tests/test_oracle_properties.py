@@ -1,0 +1,73 @@
+"""Size-independent properties of the codec and the reducers, checked on the
+CPU oracle with generated inputs (the GPU tests check the same properties at
+full bucket size through the C ABI)."""
+import numpy as np
+from hypothesis import given, settings
+from hypothesis import strategies as st
+from hypothesis.extra import numpy as hnp
+
+LIMIT = float(np.float32(2.0 ** 99))
+finite_f32 = st.floats(min_value=-LIMIT, max_value=LIMIT, allow_nan=False, allow_infinity=False, width=32)
+vectors_f32 = hnp.arrays(np.float32, st.integers(1, 700), elements=finite_f32)
+blocks = st.sampled_from((0, 32, 96, 128))
+
+
+@settings(max_examples=60, deadline=None)
+@given(vectors_f32, blocks)
+def test_quantisation_error_is_at_most_half_a_step(oracle, values, block):
+    payload, scales = oracle.encode(values, block, strict=False)
+    decoded = oracle.decode(payload, scales, block, strict=False)
+    eb = values.size if block == 0 or block >= values.size else block
+    step = np.repeat(scales, eb)[:values.size].astype(np.float64)
+    error = np.abs(values.astype(np.float64) - decoded.astype(np.float64))
+    assert np.all(error <= 0.5 * step * (1 + 1e-4) + 1e-45)
+    assert np.all(np.abs(payload.astype(np.int16)) <= 127)
+
+
+@settings(max_examples=60, deadline=None)
+@given(vectors_f32, blocks)
+def test_re_encoding_the_decode_reproduces_the_payload(oracle, values, block):
+    payload, scales = oracle.encode(values, block, strict=False)
+    decoded = oracle.decode(payload, scales, block, strict=False)
+    again, _ = oracle.encode(decoded, block, strict=False)
+    assert np.array_equal(payload, again)
+
+
+@settings(max_examples=60, deadline=None)
+@given(hnp.arrays(np.float32, st.integers(1, 300),
+                  elements=st.floats(min_value=-1024.0, max_value=1024.0, allow_nan=False, width=32)),
+       st.integers(-20, 20), blocks)
+def test_power_of_two_scaling_moves_only_the_scales(oracle, values, exponent, block):
+    # normal range, no underflow: x * 2^k has the same codes and scales * 2^k
+    values = np.where(np.abs(values) < 1e-20, 0, values).astype(np.float32)
+    factor = np.float32(2.0 ** exponent)
+    payload, scales = oracle.encode(values, block, strict=False)
+    scaled_payload, scaled_scales = oracle.encode(values * factor, block, strict=False)
+    assert np.array_equal(payload, scaled_payload)
+    nonzero = scales != 1.0
+    assert np.array_equal(scaled_scales[nonzero], scales[nonzero] * factor)
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.integers(1, 400), st.integers(0, 2 ** 31 - 1), blocks)
+def test_two_rank_reduce_is_symmetric_and_replicas_agree(oracle, n, seed, block):
+    a = oracle.generate_gradient(n, seed, 0)
+    b = oracle.generate_gradient(n, seed, 1)
+    ab = oracle.allreduce_bfp8([a, b], block, 0.5)
+    ba = oracle.allreduce_bfp8([b, a], block, 0.5)
+    assert np.array_equal(ab[0], ba[0]) and np.array_equal(ab[1], ba[1])      # fp32 add commutes
+    # the fp32 result is exactly the decode of the result payload (decode cache)
+    assert np.array_equal(ab[2], oracle.decode(ab[0], ab[1], block, strict=False))
+
+
+@settings(max_examples=40, deadline=None)
+@given(hnp.arrays(np.float32, st.integers(1, 500), elements=finite_f32))
+def test_bf16_round_trip_and_monotonic(oracle, values):
+    bits = oracle.bf16_encode(values, 1)
+    back = oracle.bf16_decode(bits)
+    again = oracle.bf16_encode(back, 1)
+    assert np.array_equal(bits, again)                                    # idempotent
+    relative = np.abs(back.astype(np.float64) - values.astype(np.float64))
+    assert np.all(relative <= np.abs(values.astype(np.float64)) * 2.0 ** -8 + 5e-41)   # half a bf16 subnormal step
+    order = np.argsort(values, kind="stable")
+    assert np.all(np.diff(back[order].astype(np.float64)) >= 0)              # rounding is monotonic

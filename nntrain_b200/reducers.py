@@ -509,25 +509,3 @@ class Bf16ArenaAllReduce:
         torch.cuda.synchronize(self.group.device)
         self.values = None
         self.buffer.close()
-
-
-def smoke_check(oracle) -> None:
-    """Two emulated ranks on one GPU: the owner kernel against the oracle."""
-    import numpy as np
-    n, block = 70001, 32
-    gradients = [oracle.generate_gradient(n, 0xB2000001, r) for r in range(2)]
-    payloads, scales = [], []
-    for g in gradients:
-        p = torch.empty(n, dtype=torch.int8, device="cuda")
-        s = torch.empty((n + block - 1) // block, dtype=torch.float32, device="cuda")
-        CudaBfp8Native.block_encode(0, torch.from_numpy(g).cuda(), p, s, block)
-        payloads.append(p)
-        scales.append(s)
-    for rank in range(2):
-        first, end = shard_range(n, 2, rank)
-        reduce_shards_bfp8(0, payloads, scales, payloads, scales, first, end, block, 0.5)
-    torch.cuda.synchronize()
-    expect_payload, expect_scales, _, _ = oracle.allreduce_bfp8(gradients, block, 0.5)
-    for p, s in zip(payloads, scales):
-        assert np.array_equal(p.cpu().numpy(), expect_payload), "reduced payload differs from the oracle"
-        assert np.array_equal(s.cpu().numpy().view(np.uint32), expect_scales.view(np.uint32)), "scales differ"

@@ -508,10 +508,28 @@ def main():
 
     # -- end to end: pinned host buffers in, encoded result out -----------------------------
     e2e = None
-    if not args.no_e2e:
-        host_gradient = torch.empty(E, dtype=torch.float32, pin_memory=True)
-        host_payload = torch.empty(E, dtype=torch.int8, pin_memory=True)
-        host_scales = torch.empty(step.scale_count, dtype=torch.float32, pin_memory=True)
+    run_e2e = not args.no_e2e
+    if run_e2e:
+        # Every rank must enter the collective part or none: agree first on
+        # whether the pinned host buffers could be had everywhere.
+        try:
+            host_gradient = torch.empty(E, dtype=torch.float32, pin_memory=True)
+            host_payload = torch.empty(E, dtype=torch.int8, pin_memory=True)
+            host_scales = torch.empty(step.scale_count, dtype=torch.float32, pin_memory=True)
+            have_buffers = 1.0
+        except RuntimeError as error:
+            print(f"rank {rank}: no pinned host buffers for the end-to-end leg: {error}", file=sys.stderr)
+            host_gradient = host_payload = host_scales = None
+            have_buffers = 0.0
+        if world > 1:
+            agreed = torch.tensor([have_buffers], dtype=torch.float64)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+            have_buffers = float(agreed.item())
+        if have_buffers == 0.0:
+            run_e2e = False
+            e2e = {"unavailable": "pinned host buffers could not be allocated on every rank"}
+            host_gradient = host_payload = host_scales = None
+    if run_e2e:
         host_gradient.copy_(arena)
         e2e_chunk = 64 << 20
         e2e_step = step if (step.chunk <= e2e_chunk) else None

@@ -235,3 +235,93 @@ def test_fused_squared_sum_cache_is_one_shot_and_version_checked(oracle):
         assert norm == expect_norm and c == expect_c
     with pytest.raises(ArgumentError):
         clip_decision(1.0, 0.0)
+
+
+def test_hundred_lifecycles_with_injected_host_faults_leave_no_state_behind():
+    # after NNtrain.Core.Tests/CudaGradientHostPipelineStressTests.cs:9-171: step
+    # lifecycles with faults injected on the host (early abort, abort after some
+    # buckets, duplicate notification, non-finite completion); the plan must
+    # reopen cleanly every time and count only the completed steps
+    import random
+    numels = decoder_tensor_list()
+    plan = GradientStepPlan(numels, devices=[0, 1, 2, 3])
+    rng = random.Random(20240917)
+    completed = 0
+    for lifecycle in range(100):
+        fault = rng.choice(("none", "early_abort", "mid_abort", "duplicate", "non_finite"))
+        step = plan.begin_step()
+        if fault == "early_abort":
+            plan.abort(step)
+            continue
+        plan.begin_device_step(step)
+        order = list(range(len(numels)))
+        rng.shuffle(order)
+        stop_after = rng.randrange(1, len(order)) if fault in ("mid_abort", "duplicate") else len(order)
+        enqueued = []
+        for tensor in order[:stop_after]:
+            plan.notify_gradient_ready(tensor, step)
+            while (bucket := plan.next_enqueueable(step)) >= 0:
+                enqueued.append(bucket)
+        assert enqueued == sorted(enqueued, reverse=True)
+        if fault == "duplicate":
+            with pytest.raises(InvalidOperationError, match="notified twice"):
+                plan.notify_gradient_ready(order[0], step)
+        if fault in ("mid_abort", "duplicate"):
+            with pytest.raises(InvalidOperationError):
+                plan.complete(step)
+            plan.abort(step)
+            assert plan.coherence_snapshot(0)["pending_step"] == 0
+            continue
+        if fault == "non_finite":
+            with pytest.raises(InvalidOperationError, match="non-finite"):
+                plan.complete(step, non_finite=True)
+            plan.abort(step)
+            continue
+        plan.complete(step)
+        completed += 1
+        plan.optimizer_validate_and_consume()
+    assert plan.completed_steps == completed > 10
+    plan.close()
+
+
+def test_concurrent_notifications_are_exactly_once():
+    # leaves are notified from several host threads (the reference has one
+    # worker thread per device plus the autograd thread); every tensor must be
+    # accepted exactly once and every bucket become ready exactly once
+    import threading
+    numels = [1000] * 400
+    plan = GradientStepPlan(numels, devices=[0, 1], target_bucket_elements=10_000)
+    step = plan.begin_step()
+    plan.begin_device_step(step)
+    accepted, rejected, ready = [], [], []
+    lock = threading.Lock()
+
+    def worker(seed: int) -> None:
+        import random
+        order = list(range(len(numels)))
+        random.Random(seed).shuffle(order)
+        for tensor in order:
+            try:
+                bucket = plan.notify_gradient_ready(tensor, step)
+                with lock:
+                    accepted.append(tensor)
+                    if bucket >= 0:
+                        ready.append(bucket)
+            except InvalidOperationError:
+                with lock:
+                    rejected.append(tensor)
+
+    threads = [threading.Thread(target=worker, args=(seed,)) for seed in range(4)]
+    for thread in threads:
+        thread.start()
+    for thread in threads:
+        thread.join()
+    assert sorted(accepted) == list(range(len(numels)))          # each tensor once
+    assert len(rejected) == 3 * len(numels)                      # every other attempt refused
+    assert sorted(ready) == list(range(plan.bucket_count))       # each bucket ready once
+    enqueued = []
+    while (bucket := plan.next_enqueueable(step)) >= 0:
+        enqueued.append(bucket)
+    assert enqueued == list(range(plan.bucket_count - 1, -1, -1))
+    plan.complete(step)
+    plan.close()

@@ -173,7 +173,8 @@ def test_block_encode_fused_outputs(cuda, oracle, block):
 
 def test_encode_decode_encode_is_idempotent_at_full_bucket_size(cuda):
     """Size-independent property at a 64 Mi-element bucket: re-encoding the
-    decode reproduces payload and scales."""
+    decode reproduces the payload, and the scales up to the one rounding the
+    format allows."""
     n = 64 << 20
     torch.manual_seed(7)
     src = torch.randn(n, device="cuda") * 1e-3
@@ -186,7 +187,14 @@ def test_encode_decode_encode_is_idempotent_at_full_bucket_size(cuda):
     scales2 = torch.empty_like(scales)
     CudaBfp8Native.block_encode(0, decoded, payload2, scales2, 32)
     torch.cuda.synchronize()
+    top0 = payload.view(-1, 32).to(torch.int16).abs().amax(dim=1)
     assert torch.equal(payload, payload2)
+    # The second scale is the IEEE quotient of the decoded maximum, 127 * scale
+    # (one binary32 multiply), by 127: equal to the first for most significands,
+    # one unit in the last place away for the rest; all-zero blocks keep 1.
+    expect2 = torch.where(top0 == 0, torch.ones_like(scales), (scales * 127.0) / 127.0)
+    assert torch.equal(scales2.view(torch.int32), expect2.view(torch.int32))
+    assert bool(((scales2.view(torch.int32) - scales.view(torch.int32)).abs() <= 1).all())
     # |x - decode| <= scale/2 per block, scale = max/127
     err = (src - decoded).abs().view(-1, 32).amax(dim=1)
     assert bool((err <= scales * 0.50002).all())

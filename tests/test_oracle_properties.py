@@ -2,6 +2,7 @@
 CPU oracle with generated inputs (the GPU tests check the same properties at
 full bucket size through the C ABI)."""
 import numpy as np
+import pytest
 from hypothesis import given, settings
 from hypothesis import strategies as st
 from hypothesis.extra import numpy as hnp
@@ -28,9 +29,21 @@ def test_quantisation_error_is_at_most_half_a_step(oracle, values, block):
 @given(vectors_f32, blocks)
 def test_re_encoding_the_decode_reproduces_the_payload(oracle, values, block):
     payload, scales = oracle.encode(values, block, strict=False)
+    if np.any(scales == 0.0):
+        # A block whose max/127 underflows to zero has no valid encoding: the
+        # reference codec throws there (NNtrain.Core/Tensors/Bfp8Quantization.cs:120-127),
+        # and so does the oracle in strict mode; the property is not defined.
+        with pytest.raises(oracle.OracleError) as caught:
+            oracle.encode(values, block, strict=True)
+        assert caught.value.code == oracle.ERR_BAD_SCALE
+        return
     decoded = oracle.decode(payload, scales, block, strict=False)
-    again, _ = oracle.encode(decoded, block, strict=False)
+    again, scales_again = oracle.encode(decoded, block, strict=False)
     assert np.array_equal(payload, again)
+    # The scale may move by one unit in the last place (fl(fl(127 s) / 127) != s
+    # for about 0.8 % of significands), never further.
+    assert np.all(np.abs(scales_again.astype(np.float64) - scales.astype(np.float64))
+                  <= np.spacing(scales).astype(np.float64))
 
 
 @settings(max_examples=60, deadline=None)

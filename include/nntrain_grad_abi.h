@@ -65,16 +65,16 @@ int nntrain_cuda_set_device(int device);
 int nntrain_cuda_use_external_stream(void* stream);
 
 /* ABI minor 36; no counterpart in the reference (its kernels use fixed
- * grids).  Launch shapes for overlapping the collective with the codec kernels
- * of neighbouring chunks.  codec_iterations_per_cta: n > 0 = short-lived CTAs
- * of n iterations each for the encode / decode kernels (default 2, also the
- * fastest for a kernel running alone), 0 = persistent grids.
- * collective_ctas: 0 = the all-reduce kernels fill the machine, n > 0 = at most
- * n CTAs.  Process-wide. */
+ * grids).  Process-wide defaults of the launch shapes.
+ * codec_iterations_per_cta: n > 0 = short-lived CTAs of n iterations each for
+ * the encode / decode kernels (default 2, also the fastest for a kernel
+ * running alone), 0 = persistent grids.  collective_ctas: what a group created
+ * afterwards starts with (see nntrain_gradient_group_configure); default 0. */
 int nntrain_gradient_configure(int codec_iterations_per_cta, int collective_ctas);
-/* ABI minor 36; no counterpart in the reference.  How the all-reduce kernels
- * fetch their inputs: 1 (default) = cp.async rings in shared memory, 0 =
- * register prefetch.  Same results either way. */
+/* ABI minor 36; no counterpart in the reference.  How the owner / all-reduce
+ * kernels fetch their inputs when no group says otherwise: 1 (default) =
+ * cp.async rings in shared memory, 0 = register prefetch.  Same results
+ * either way. */
 int nntrain_gradient_configure_collective(int asynchronous_copies);
 /* ABI minor 36; no counterpart in the reference.  Most CTAs a persistent
  * encode / decode grid may use (only with codec_iterations_per_cta == 0);
@@ -234,8 +234,9 @@ int nntrain_gradient_clip_coefficient(int device, const double* squared_sum, flo
 /* ABI minor 36.  Whole-arena clip.  kind 0: fp32 *= c (nn.cs:72-78); kind 1:
  * bf16 = rn(f32 * c) (pure_bfloat16_gradients.cu:337-348); kind 2: values is
  * the fp32 scale sidecar, scale = fmaxf(scale * c, FLT_MIN), payload untouched
- * (tensor_kernels.cu:1075-1082).  With a non-null `coefficient` (kind 2) the
- * multiplier is coefficient[1] read on the device. */
+ * (tensor_kernels.cu:1075-1082).  With a non-null `coefficient` the multiplier
+ * is coefficient[1] read on the device (the output of
+ * nntrain_gradient_clip_coefficient) and a value of exactly 1 touches nothing. */
 int nntrain_gradient_clip_apply(int device, int kind, void* values, long long count, float multiplier,
                                 const float* coefficient, nntrain_stream_t stream);
 
@@ -261,6 +262,15 @@ int nntrain_gradient_group_unique_id(void* id128);
 int nntrain_gradient_group_create(const void* id128, int world, int rank, int device, void** group);
 /* Destroys the communicator and the group's device scratch. */
 int nntrain_gradient_group_destroy(void* group);
+/* Launch shape of ONE group's all-reduce kernels (either kind of group), so
+ * that two reducers in a process do not retune each other.  collective_ctas:
+ * 0 = fill the machine, n > 0 = at most n CTAs.  asynchronous_copies: 1 =
+ * cp.async rings, 0 = register prefetch.  exclusive_sms (needs
+ * asynchronous_copies): every CTA asks for a whole SM's shared memory, so
+ * collective_ctas SMs belong to the all-reduce while it runs and the encode /
+ * decode kernels of neighbouring chunks never share an SM with it. */
+int nntrain_gradient_group_configure(void* group, int collective_ctas, int asynchronous_copies,
+                                     int exclusive_sms);
 /* Host-side liveness: 0 or the communicator's asynchronous error; never blocks. */
 int nntrain_gradient_group_poll(void* group);
 /* Abandon the communicator without waiting (a peer was declared lost). */
@@ -323,6 +333,33 @@ int nntrain_gradient_stream_wait_event(nntrain_stream_t stream, nntrain_event_t 
 int nntrain_gradient_allreduce_bf16(
     void* group, unsigned short* const* values_by_rank, long long length, float reduction_scale,
     double* squared_sum, int mode, int phase, unsigned short* staging, nntrain_stream_t stream);
+
+/* ---- N-rank all-reduce, ONE process driving all devices (ABI minor 36) ------
+ * The host model of the reference's engine: one worker thread per device
+ * (NNtrain.Core/Training/CudaReplicaExecutor.cs:29-116,339-369), the worker
+ * that arrives last enqueues the cross-device work
+ * (NNtrain.Core/Training/CudaBfp8GradientAllReduce.cs:352-363).  Buffers are
+ * plain device allocations; peer access is enabled at creation; ranks are
+ * ordered by events only, so one thread can enqueue the whole step. */
+
+/* devices[r] is rank r's device; a device may repeat (those ranks share it). */
+int nntrain_gradient_local_group_create(int ranks, const int* devices, void** group);
+/* Waits for the devices to go idle, then frees the group's scratch and events. */
+int nntrain_gradient_local_group_destroy(void* group);
+/* In-place BFP8 all-reduce of one encoded arena (or chunk) on every rank;
+ * streams[r] is rank r's communication stream.  All tables are host arrays
+ * with one entry per rank; squared_sum_by_rank / finite_status_by_rank may be
+ * null.  phase as in nntrain_gradient_allreduce_bfp8.  Replaces the pull /
+ * reduce / push of NNtrain.Cuda/native/tensor_kernels.cu:3935-4038 and
+ * NNtrain.Cuda/native/gradient_collectives.cu:311-357 for N devices. */
+int nntrain_gradient_local_allreduce_bfp8(
+    void* group, signed char* const* payload_by_rank, float* const* scales_by_rank, long long length,
+    int block_size, float reduction_scale, double* const* squared_sum_by_rank,
+    int* const* finite_status_by_rank, int phase, const nntrain_stream_t* streams);
+/* bf16 twin (gradient_collectives.cu:272-309 for N devices). */
+int nntrain_gradient_local_allreduce_bf16(
+    void* group, unsigned short* const* values_by_rank, long long length, float reduction_scale,
+    double* const* squared_sum_by_rank, int phase, const nntrain_stream_t* streams);
 
 #ifdef __cplusplus
 }

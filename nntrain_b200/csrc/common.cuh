@@ -38,6 +38,15 @@ enum Operation : std::uint32_t {
     kOpCapabilities = 25,
     kOpBfp8Quantize = 26,
     kOpBfp8DequantizeF32 = 27,
+    // ABI minor 36 (no counterpart in the reference's numbering)
+    // 200: the allocation-free owner reduce (no_alloc.cu)
+    kOpGradientPeerMemory = 210,
+    kOpGradientGroup = 211,
+    kOpGradientReduceShards = 212,
+    kOpGradientAllReduce = 213,
+    kOpGradientLocalGroup = 214,
+    kOpGradientLocalAllReduce = 215,
+    kOpGradientPublishTensors = 216,
 };
 
 struct ErrorInfo {            // layout of nntrain_native_error_info (:74-82)
@@ -128,15 +137,6 @@ int resident_ctas_per_sm() {
     return cached;
 }
 #endif
-
-// Grid for the all-reduce kernels.
-inline int collective_grid_for(long long work_items) {
-    if (work_items < 1) work_items = 1;
-    long long cap = launch_policy().collective_ctas;
-    if (cap <= 0) cap = static_cast<long long>(sm_count()) * kCtasPerSmDefault;
-    return static_cast<int>(work_items < cap ? work_items : cap);
-}
-
 
 // ---- device helpers -------------------------------------------------------
 #ifdef __CUDACC__

@@ -102,7 +102,8 @@ const NcclApi* nccl() {
 inline int nccl_status(ncclResult_t r) { return r == ncclSuccess ? 0 : kNcclStatusBase + static_cast<int>(r); }
 
 // ---- group ---------------------------------------------------------------------
-struct Group {
+struct Group : GroupHeader {
+    Group() : GroupHeader{kKindProcessGroup, CollectiveShape{0, 1, 0}} {}
     int world = 1;
     int rank = 0;
     int device = 0;
@@ -191,7 +192,7 @@ using namespace ngb;
 // ---- peer-visible memory (CUDA IPC) ----------------------------------------------
 // Allocates `bytes` on `device` with cudaMalloc and writes the 64-byte IPC
 // handle other processes open with nntrain_gradient_peer_open.
-NNTRAIN_EXPORT int nntrain_gradient_peer_alloc(int device, long long bytes, void** pointer, void* handle64) {
+static int gradient_peer_alloc_impl(int device, long long bytes, void** pointer, void* handle64) {
     if (!pointer || !handle64 || bytes <= 0) return static_cast<int>(cudaErrorInvalidValue);
     int status = select_device(device);
     if (status != cudaSuccess) return status;
@@ -207,7 +208,7 @@ NNTRAIN_EXPORT int nntrain_gradient_peer_alloc(int device, long long bytes, void
     return 0;
 }
 
-NNTRAIN_EXPORT int nntrain_gradient_peer_free(int device, void* pointer) {
+static int gradient_peer_free_impl(int device, void* pointer) {
     int status = select_device(device);
     if (status != cudaSuccess) return status;
     return static_cast<int>(cudaFree(pointer));
@@ -215,7 +216,7 @@ NNTRAIN_EXPORT int nntrain_gradient_peer_free(int device, void* pointer) {
 
 // Maps another process's allocation into this process on `device` (peer
 // access is enabled lazily by the runtime).
-NNTRAIN_EXPORT int nntrain_gradient_peer_open(int device, const void* handle64, void** pointer) {
+static int gradient_peer_open_impl(int device, const void* handle64, void** pointer) {
     if (!handle64 || !pointer) return static_cast<int>(cudaErrorInvalidValue);
     int status = select_device(device);
     if (status != cudaSuccess) return status;
@@ -224,7 +225,7 @@ NNTRAIN_EXPORT int nntrain_gradient_peer_open(int device, const void* handle64, 
     return static_cast<int>(cudaIpcOpenMemHandle(pointer, handle, cudaIpcMemLazyEnablePeerAccess));
 }
 
-NNTRAIN_EXPORT int nntrain_gradient_peer_close(int device, void* pointer) {
+static int gradient_peer_close_impl(int device, void* pointer) {
     int status = select_device(device);
     if (status != cudaSuccess) return status;
     return static_cast<int>(cudaIpcCloseMemHandle(pointer));
@@ -243,40 +244,9 @@ NNTRAIN_EXPORT int nntrain_gradient_group_unique_id(void* id128) {
     return status;
 }
 
-// Collective over all ranks.  world == 1 needs no id and no NCCL.
-NNTRAIN_EXPORT int nntrain_gradient_group_create(const void* id128, int world, int rank, int device, void** group) {
-    if (!group || world < 1 || world > kMaxRanks || rank < 0 || rank >= world || (world > 1 && !id128))
-        return static_cast<int>(cudaErrorInvalidValue);
-    *group = nullptr;
-    int status = select_device(device);
-    if (status != cudaSuccess) return status;
-    Group* g = new (std::nothrow) Group();
-    if (!g) return static_cast<int>(cudaErrorMemoryAllocation);
-    g->world = world;
-    g->rank = rank;
-    g->device = device;
-    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&g->scratch), 4 * sizeof(double));
-    if (e == cudaSuccess) e = cudaMemset(g->scratch, 0, 4 * sizeof(double));
-    for (int w = 0; e == cudaSuccess && w < 2; ++w) {
-        e = cudaStreamCreateWithFlags(&g->wire[w], cudaStreamNonBlocking);
-        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&g->join[w], cudaEventDisableTiming);
-    }
-    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&g->fork, cudaEventDisableTiming);
-    if (e != cudaSuccess) { delete g; return static_cast<int>(e); }
-    if (world > 1) {
-        const NcclApi* api = nccl();
-        if (!api) { cudaFree(g->scratch); delete g; return kNcclMissing; }
-        ncclUniqueId id;
-        std::memcpy(&id, id128, sizeof(id));
-        status = nccl_status(api->CommInitRank(&g->comm, world, id, rank));
-        if (status != 0) { cudaFree(g->scratch); delete g; return status; }
-    }
-    *group = g;
-    return 0;
-}
+namespace {
 
-NNTRAIN_EXPORT int nntrain_gradient_group_destroy(void* group) {
-    Group* g = static_cast<Group*>(group);
+int group_destroy_impl(Group* g) {
     if (!g) return 0;
     int first = select_device(g->device);
     if (g->comm) {
@@ -291,6 +261,74 @@ NNTRAIN_EXPORT int nntrain_gradient_group_destroy(void* group) {
     if (g->fork) cudaEventDestroy(g->fork);
     delete g;
     return first;
+}
+
+int group_create_impl(const void* id128, int world, int rank, int device, void** group) {
+    if (!group || world < 1 || world > kMaxRanks || rank < 0 || rank >= world || (world > 1 && !id128))
+        return static_cast<int>(cudaErrorInvalidValue);
+    *group = nullptr;
+    int status = select_device(device);
+    if (status != cudaSuccess) return status;
+    Group* g = new (std::nothrow) Group();
+    if (!g) return static_cast<int>(cudaErrorMemoryAllocation);
+    g->world = world;
+    g->rank = rank;
+    g->device = device;
+    g->shape = default_collective_shape();
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&g->scratch), 4 * sizeof(double));
+    if (e == cudaSuccess) e = cudaMemset(g->scratch, 0, 4 * sizeof(double));
+    for (int w = 0; e == cudaSuccess && w < 2; ++w) {
+        e = cudaStreamCreateWithFlags(&g->wire[w], cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&g->join[w], cudaEventDisableTiming);
+    }
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&g->fork, cudaEventDisableTiming);
+    status = static_cast<int>(e);
+    if (status == 0 && world > 1) {
+        const NcclApi* api = nccl();
+        if (!api) status = kNcclMissing;
+        else {
+            ncclUniqueId id;
+            std::memcpy(&id, id128, sizeof(id));
+            status = nccl_status(api->CommInitRank(&g->comm, world, id, rank));
+            if (status != 0) g->comm = nullptr;
+        }
+    }
+    // one way out for every failure: whatever was created is released
+    if (status != 0) { group_destroy_impl(g); return status; }
+    *group = g;
+    return 0;
+}
+
+}  // namespace
+
+// Collective over all ranks.  world == 1 needs no id and no NCCL.  The
+// group's launch shape for its all-reduce kernels starts as the process-wide
+// default and is changed with nntrain_gradient_group_configure.
+NNTRAIN_EXPORT int nntrain_gradient_group_create(const void* id128, int world, int rank, int device, void** group) {
+    return complete(kOpGradientGroup, device, group_create_impl(id128, world, rank, device, group));
+}
+
+NNTRAIN_EXPORT int nntrain_gradient_group_destroy(void* group) {
+    Group* g = static_cast<Group*>(group);
+    if (!g) return 0;
+    const int device = g->device;
+    return complete(kOpGradientGroup, device, group_destroy_impl(g));
+}
+
+// Launch shape of this group's all-reduce kernels (peer transport).
+// collective_ctas: 0 = fill the machine, n > 0 = at most n CTAs.
+// asynchronous_copies: 1 = cp.async rings, 0 = register prefetch.
+// exclusive_sms: 1 (with asynchronous_copies) = every CTA takes a whole SM, so
+// collective_ctas SMs belong to the all-reduce while it runs and the codec
+// kernels of the neighbouring chunks keep the rest to themselves.
+NNTRAIN_EXPORT int nntrain_gradient_group_configure(void* group, int collective_ctas, int asynchronous_copies,
+                                                    int exclusive_sms) {
+    GroupHeader* header = static_cast<GroupHeader*>(group);
+    if (!header || (header->kind != kKindProcessGroup && header->kind != kKindLocalGroup) || collective_ctas < 0)
+        return complete(kOpGradientGroup, -1, static_cast<int>(cudaErrorInvalidValue));
+    header->shape = CollectiveShape{collective_ctas, asynchronous_copies != 0 ? 1 : 0,
+                                    (exclusive_sms != 0 && asynchronous_copies != 0) ? 1 : 0};
+    return 0;
 }
 
 // Host-side liveness check: 0 = healthy, otherwise the communicator's
@@ -333,7 +371,7 @@ NNTRAIN_EXPORT int nntrain_gradient_shard_range(long long length, int world, int
 // r = reduction_scale * (rank-ordered fp32 sum of decoded inputs) over
 // [first_value, end_value), re-encoded in blocks of block_size (32/64/128)
 // and stored to every output.  first_value must be a multiple of block_size.
-NNTRAIN_EXPORT int nntrain_gradient_reduce_shards_bfp8(
+static int gradient_reduce_shards_bfp8_impl(
     int device, int inputs, const signed char* const* payloads, const float* const* scales, int outputs,
     signed char* const* out_payloads, float* const* out_scales, long long first_value, long long end_value,
     int block_size, float reduction_scale, double* squared_sum, int* finite_status, cudaStream_t stream) {
@@ -354,7 +392,7 @@ NNTRAIN_EXPORT int nntrain_gradient_reduce_shards_bfp8(
 // bf16 twin: fp32 accumulate in rank order, optional fp32 output (local),
 // bf16 round-to-nearest-even outputs, optional sum of squares of the bf16
 // result (square_of_bf16 != 0) or of the fp32 sum.
-NNTRAIN_EXPORT int nntrain_gradient_reduce_shards_bf16(
+static int gradient_reduce_shards_bf16_impl(
     int device, int inputs, const unsigned short* const* values, int outputs, unsigned short* const* out_values,
     float* reduced, long long first_value, long long end_value, float reduction_scale, double* squared_sum,
     int square_of_bf16, cudaStream_t stream) {
@@ -392,7 +430,7 @@ NNTRAIN_EXPORT int nntrain_gradient_reduce_shards_bf16(
 // through staging_payload / staging_scales (capacity: world shards).
 // Collective: every rank must call it with the same length / block / mode, in
 // the same order relative to other calls on the group.
-NNTRAIN_EXPORT int nntrain_gradient_allreduce_bfp8(
+static int gradient_allreduce_bfp8_impl(
     void* group, signed char* const* payload_by_rank, float* const* scales_by_rank, long long length,
     int block_size, float reduction_scale, double* squared_sum, int* finite_status, int mode, int phase,
     signed char* staging_payload, float* staging_scales, cudaEvent_t previous_final, cudaStream_t stream) {
@@ -417,6 +455,8 @@ NNTRAIN_EXPORT int nntrain_gradient_allreduce_bfp8(
         if ((e = cudaPeekAtLastError()) != cudaSuccess) return static_cast<int>(e);
     }
 
+    // owner kernels that read staged (local) shards are short: they fill the machine
+    const CollectiveShape local_shape{0, g->shape.asynchronous, 0};
     EncodedShards shards{};
     shards.inputs = world;
     if (mode == 0 || world == 1) {
@@ -435,7 +475,7 @@ NNTRAIN_EXPORT int nntrain_gradient_allreduce_bfp8(
         }
         if (end > first) {
             e = launch_bfp8_reduce_reencode(shards, first, end, block_size, reduction_scale, g->scratch,
-                                            shard_flag, stream);
+                                            shard_flag, stream, &g->shape);
             if (e != cudaSuccess) return static_cast<int>(e);
         }
     } else if (mode == 2) {
@@ -479,7 +519,7 @@ NNTRAIN_EXPORT int nntrain_gradient_allreduce_bfp8(
             shards.out_payload[0] = own_payload;
             shards.out_scales[0] = own_scales;
             e = launch_bfp8_reduce_reencode(shards, first, end, block_size, reduction_scale, g->scratch,
-                                            shard_flag, stream);
+                                            shard_flag, stream, &local_shape);
             if (e != cudaSuccess) return static_cast<int>(e);
             if ((e = fork_wire(g, stream)) != cudaSuccess) return static_cast<int>(e);
             for (int step = 1; step < world; ++step) {
@@ -538,7 +578,7 @@ NNTRAIN_EXPORT int nntrain_gradient_allreduce_bfp8(
             shards.out_payload[0] = own_payload;
             shards.out_scales[0] = own_scales;
             e = launch_bfp8_reduce_reencode(shards, first, end, block_size, reduction_scale, g->scratch,
-                                            shard_flag, stream);
+                                            shard_flag, stream, &local_shape);
             if (e != cudaSuccess) return static_cast<int>(e);
         }
         // all-gather of the reduced shards, in place in the arena
@@ -576,7 +616,7 @@ NNTRAIN_EXPORT int nntrain_gradient_allreduce_bfp8(
 // rounded to bf16 (nearest even) and stored into every rank's arena;
 // *squared_sum += sum of squares of the bf16 result.  Modes as above
 // (staging: world shards of bf16).
-NNTRAIN_EXPORT int nntrain_gradient_allreduce_bf16(
+static int gradient_allreduce_bf16_impl(
     void* group, unsigned short* const* values_by_rank, long long length, float reduction_scale,
     double* squared_sum, int mode, int phase, unsigned short* staging, cudaStream_t stream) {
     Group* g = static_cast<Group*>(group);
@@ -608,7 +648,7 @@ NNTRAIN_EXPORT int nntrain_gradient_allreduce_bf16(
             io.out_bf16[k] = values_by_rank[k];
         }
         if (end > first) {
-            e = launch_bf16_reduce(io, nullptr, first, end, reduction_scale, g->scratch, true, stream);
+            e = launch_bf16_reduce(io, nullptr, first, end, reduction_scale, g->scratch, true, stream, &g->shape);
             if (e != cudaSuccess) return static_cast<int>(e);
         }
     } else {
@@ -654,7 +694,7 @@ NNTRAIN_EXPORT int nntrain_gradient_allreduce_bf16(
 // Sums `count` doubles over the ranks in place (stream-ordered); with
 // count == 0 it is a pure barrier.  For host-side quantities that ride along
 // with a step (global norm pieces, flags).
-NNTRAIN_EXPORT int nntrain_gradient_group_sum(void* group, double* values, int count, cudaStream_t stream) {
+static int gradient_group_sum_impl(void* group, double* values, int count, cudaStream_t stream) {
     Group* g = static_cast<Group*>(group);
     if (!g || count < 0 || (count > 0 && !values)) return static_cast<int>(cudaErrorInvalidValue);
     if (g->world == 1) return 0;
@@ -672,4 +712,50 @@ NNTRAIN_EXPORT int nntrain_gradient_group_sum(void* group, double* values, int c
 NNTRAIN_EXPORT int nntrain_gradient_stream_wait_event(cudaStream_t stream, cudaEvent_t event) {
     if (!event) return static_cast<int>(cudaErrorInvalidValue);
     return static_cast<int>(cudaStreamWaitEvent(stream, event, 0));
+}
+
+// ---- exports: every failure is recorded in the error ring (nntrain_last_error) -----------
+NNTRAIN_EXPORT int nntrain_gradient_peer_alloc(int device, long long bytes, void** pointer, void* handle64) {
+    return complete(kOpGradientPeerMemory, device,
+                    gradient_peer_alloc_impl(device, bytes, pointer, handle64));
+}
+
+NNTRAIN_EXPORT int nntrain_gradient_peer_free(int device, void* pointer) {
+    return complete(kOpGradientPeerMemory, device,
+                    gradient_peer_free_impl(device, pointer));
+}
+
+NNTRAIN_EXPORT int nntrain_gradient_peer_open(int device, const void* handle64, void** pointer) {
+    return complete(kOpGradientPeerMemory, device,
+                    gradient_peer_open_impl(device, handle64, pointer));
+}
+
+NNTRAIN_EXPORT int nntrain_gradient_peer_close(int device, void* pointer) {
+    return complete(kOpGradientPeerMemory, device,
+                    gradient_peer_close_impl(device, pointer));
+}
+
+NNTRAIN_EXPORT int nntrain_gradient_reduce_shards_bfp8(int device, int inputs, const signed char* const* payloads, const float* const* scales, int outputs, signed char* const* out_payloads, float* const* out_scales, long long first_value, long long end_value, int block_size, float reduction_scale, double* squared_sum, int* finite_status, cudaStream_t stream) {
+    return complete(kOpGradientReduceShards, device,
+                    gradient_reduce_shards_bfp8_impl(device, inputs, payloads, scales, outputs, out_payloads, out_scales, first_value, end_value, block_size, reduction_scale, squared_sum, finite_status, stream));
+}
+
+NNTRAIN_EXPORT int nntrain_gradient_reduce_shards_bf16(int device, int inputs, const unsigned short* const* values, int outputs, unsigned short* const* out_values, float* reduced, long long first_value, long long end_value, float reduction_scale, double* squared_sum, int square_of_bf16, cudaStream_t stream) {
+    return complete(kOpGradientReduceShards, device,
+                    gradient_reduce_shards_bf16_impl(device, inputs, values, outputs, out_values, reduced, first_value, end_value, reduction_scale, squared_sum, square_of_bf16, stream));
+}
+
+NNTRAIN_EXPORT int nntrain_gradient_allreduce_bfp8(void* group, signed char* const* payload_by_rank, float* const* scales_by_rank, long long length, int block_size, float reduction_scale, double* squared_sum, int* finite_status, int mode, int phase, signed char* staging_payload, float* staging_scales, cudaEvent_t previous_final, cudaStream_t stream) {
+    return complete(kOpGradientAllReduce, group ? static_cast<Group*>(group)->device : -1,
+                    gradient_allreduce_bfp8_impl(group, payload_by_rank, scales_by_rank, length, block_size, reduction_scale, squared_sum, finite_status, mode, phase, staging_payload, staging_scales, previous_final, stream));
+}
+
+NNTRAIN_EXPORT int nntrain_gradient_allreduce_bf16(void* group, unsigned short* const* values_by_rank, long long length, float reduction_scale, double* squared_sum, int mode, int phase, unsigned short* staging, cudaStream_t stream) {
+    return complete(kOpGradientAllReduce, group ? static_cast<Group*>(group)->device : -1,
+                    gradient_allreduce_bf16_impl(group, values_by_rank, length, reduction_scale, squared_sum, mode, phase, staging, stream));
+}
+
+NNTRAIN_EXPORT int nntrain_gradient_group_sum(void* group, double* values, int count, cudaStream_t stream) {
+    return complete(kOpGradientGroup, group ? static_cast<Group*>(group)->device : -1,
+                    gradient_group_sum_impl(group, values, count, stream));
 }

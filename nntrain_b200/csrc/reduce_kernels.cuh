@@ -274,13 +274,21 @@ __device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_g
 template <int kPending>
 __device__ __forceinline__ void async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory"); }
 
-template <int kRanks, int kStages>
+template <int kRanks, int kStages, int kWarps>
 constexpr size_t reduce_ring_bytes() {
-    return static_cast<size_t>(kWarpsPerCta) * kStages * kRanks * 32 * (sizeof(uint4) + sizeof(float));
+    return static_cast<size_t>(kWarps) * kStages * kRanks * 32 * (sizeof(uint4) + sizeof(float));
 }
 
-template <int kBlock, int kRanks, bool kSquares, int kStages>
-__global__ void __launch_bounds__(kThreads)
+// Dynamic shared memory that makes a CTA the only one its SM can hold: every
+// CTA also reserves 1 KB for the system, and an SM has 228 KB, so a CTA asking
+// for all but 512 bytes of the 227 KB a CTA may have leaves less than that
+// 1 KB to anyone else.  An all-reduce kernel launched this way on G CTAs owns
+// G SMs outright; the codec kernels of the neighbouring chunks get the other
+// SMs and never share a memory request path with it.
+constexpr size_t kExclusiveSharedBytes = 227 * 1024 - 512;
+
+template <int kBlock, int kRanks, bool kSquares, int kStages, int kWarps>
+__global__ void __launch_bounds__(kWarps * 32)
 bfp8_reduce_reencode_async_kernel(EncodedShards shards, long long first_value, long long end_value,
                                   float reduction_scale, double* squared_sum, int* finite_status) {
     static_assert(kRanks > 0 && kStages >= 2, "compile-time rank count, at least two stages");
@@ -289,10 +297,10 @@ bfp8_reduce_reencode_async_kernel(EncodedShards shards, long long first_value, l
     const int warp_in_cta = threadIdx.x >> 5;
     // payload ring: [warp][stage][rank][lane] uint4; scale ring behind it: same shape, float
     uint4* payload_ring = ring + static_cast<size_t>(warp_in_cta) * kStages * kRanks * 32;
-    float* scale_ring = reinterpret_cast<float*>(ring + static_cast<size_t>(kWarpsPerCta) * kStages * kRanks * 32) +
+    float* scale_ring = reinterpret_cast<float*>(ring + static_cast<size_t>(kWarps) * kStages * kRanks * 32) +
                         static_cast<size_t>(warp_in_cta) * kStages * kRanks * 32;
-    const long long warp = static_cast<long long>(blockIdx.x) * kWarpsPerCta + warp_in_cta;
-    const long long warps = static_cast<long long>(gridDim.x) * kWarpsPerCta;
+    const long long warp = static_cast<long long>(blockIdx.x) * kWarps + warp_in_cta;
+    const long long warps = static_cast<long long>(gridDim.x) * kWarps;
     const long long tiles = (end_value - first_value + 511) / 512;
     double squares = 0.0;
     int non_finite = 0;
@@ -467,7 +475,65 @@ __device__ __forceinline__ unsigned short float_to_bf16_bits(float value) {
 // of squares (of the bf16-rounded value when kSquareOfBf16, else of the fp32
 // sum).  Eight values (one 128-bit load per input) per lane per step when
 // `vector_ok`, scalar otherwise.
+// kRanks > 0: number of inputs known at compile time; the loads of the NEXT
+// group of every rank are issued before the current group's arithmetic, so
+// with peer pointers a lane always has one NVLink round trip per rank in
+// flight.  kRanks == 0: runtime count, loads and arithmetic alternate.
+template <int kRanks>
+struct Bf16Group {
+    uint4 raw[kRanks > 0 ? kRanks : 1];
+};
+
+template <int kRanks>
+__device__ __forceinline__ void load_bf16_group(const Bf16Inputs& io, long long at, Bf16Group<kRanks>& group) {
+    #pragma unroll
+    for (int k = 0; k < kRanks; ++k) group.raw[k] = __ldcs(reinterpret_cast<const uint4*>(io.values[k] + at));
+}
+
+template <bool kFirst>
+__device__ __forceinline__ void accumulate_bf16x8(const uint4& raw, float (&acc)[8]) {
+    const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
+    #pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float lo = __uint_as_float(w[q] << 16), hi = __uint_as_float(w[q] & 0xffff0000u);
+        acc[2 * q] = kFirst ? lo : __fadd_rn(acc[2 * q], lo);
+        acc[2 * q + 1] = kFirst ? hi : __fadd_rn(acc[2 * q + 1], hi);
+    }
+}
+
 template <bool kSquares, bool kSquareOfBf16>
+__device__ __forceinline__ void finish_bf16x8(const Bf16Inputs& io, float* reduced, long long at, float (&acc)[8],
+                                              float reduction_scale, double& squares) {
+    #pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = __fmul_rn(reduction_scale, acc[i]);
+    if (reduced != nullptr) {
+        store_f4(reduced + at, make_float4(acc[0], acc[1], acc[2], acc[3]));
+        store_f4(reduced + at + 4, make_float4(acc[4], acc[5], acc[6], acc[7]));
+    }
+    unsigned short e[8];
+    if (io.outputs > 0 || (kSquares && kSquareOfBf16)) {
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) e[i] = float_to_bf16_bits(acc[i]);
+    }
+    if (io.outputs > 0) {
+        uint4 packed;
+        packed.x = e[0] | (static_cast<unsigned>(e[1]) << 16);
+        packed.y = e[2] | (static_cast<unsigned>(e[3]) << 16);
+        packed.z = e[4] | (static_cast<unsigned>(e[5]) << 16);
+        packed.w = e[6] | (static_cast<unsigned>(e[7]) << 16);
+        for (int d = 0; d < io.outputs; ++d)
+            *reinterpret_cast<uint4*>(io.out_bf16[d] + at) = packed;
+    }
+    if (kSquares) {
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const double v = static_cast<double>(kSquareOfBf16 ? bf16_bits_to_float(e[i]) : acc[i]);
+            squares += v * v;
+        }
+    }
+}
+
+template <int kRanks, bool kSquares, bool kSquareOfBf16>
 __global__ void __launch_bounds__(kThreads)
 bf16_reduce_kernel(Bf16Inputs io, float* reduced, long long first_value, long long end_value,
                    float reduction_scale, double* squared_sum, bool vector_ok) {
@@ -476,45 +542,33 @@ bf16_reduce_kernel(Bf16Inputs io, float* reduced, long long first_value, long lo
     const long long span = end_value - first_value;
     const long long groups = vector_ok ? span / 8 : 0;
     double squares = 0.0;
-    for (long long g = thread; g < groups; g += threads) {
-        const long long at = first_value + g * 8;
-        float acc[8];
-        for (int k = 0; k < io.inputs; ++k) {
-            const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(io.values[k] + at));
-            const unsigned w[4] = {raw.x, raw.y, raw.z, raw.w};
+    if (kRanks > 0) {
+        Bf16Group<kRanks> current, next;
+        long long g = thread;
+        if (g < groups) load_bf16_group<kRanks>(io, first_value + g * 8, current);
+        while (g < groups) {
+            const long long following = g + threads;
+            if (following < groups) load_bf16_group<kRanks>(io, first_value + following * 8, next);
+            float acc[8];
             #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float lo = __uint_as_float(w[q] << 16), hi = __uint_as_float(w[q] & 0xffff0000u);
-                acc[2 * q] = k == 0 ? lo : __fadd_rn(acc[2 * q], lo);
-                acc[2 * q + 1] = k == 0 ? hi : __fadd_rn(acc[2 * q + 1], hi);
+            for (int k = 0; k < kRanks; ++k) {
+                if (k == 0) accumulate_bf16x8<true>(current.raw[k], acc);
+                else accumulate_bf16x8<false>(current.raw[k], acc);
             }
+            finish_bf16x8<kSquares, kSquareOfBf16>(io, reduced, first_value + g * 8, acc, reduction_scale, squares);
+            current = next;
+            g = following;
         }
-        #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = __fmul_rn(reduction_scale, acc[i]);
-        if (reduced != nullptr) {
-            store_f4(reduced + at, make_float4(acc[0], acc[1], acc[2], acc[3]));
-            store_f4(reduced + at + 4, make_float4(acc[4], acc[5], acc[6], acc[7]));
-        }
-        unsigned short e[8];
-        if (io.outputs > 0 || (kSquares && kSquareOfBf16)) {
-            #pragma unroll
-            for (int i = 0; i < 8; ++i) e[i] = float_to_bf16_bits(acc[i]);
-        }
-        if (io.outputs > 0) {
-            uint4 packed;
-            packed.x = e[0] | (static_cast<unsigned>(e[1]) << 16);
-            packed.y = e[2] | (static_cast<unsigned>(e[3]) << 16);
-            packed.z = e[4] | (static_cast<unsigned>(e[5]) << 16);
-            packed.w = e[6] | (static_cast<unsigned>(e[7]) << 16);
-            for (int d = 0; d < io.outputs; ++d)
-                *reinterpret_cast<uint4*>(io.out_bf16[d] + at) = packed;
-        }
-        if (kSquares) {
-            #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const double v = static_cast<double>(kSquareOfBf16 ? bf16_bits_to_float(e[i]) : acc[i]);
-                squares += v * v;
+    } else {
+        for (long long g = thread; g < groups; g += threads) {
+            const long long at = first_value + g * 8;
+            float acc[8];
+            for (int k = 0; k < io.inputs; ++k) {
+                const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(io.values[k] + at));
+                if (k == 0) accumulate_bf16x8<true>(raw, acc);
+                else accumulate_bf16x8<false>(raw, acc);
             }
+            finish_bf16x8<kSquares, kSquareOfBf16>(io, reduced, at, acc, reduction_scale, squares);
         }
     }
     for (long long i = first_value + groups * 8 + thread; i < end_value; i += threads) {
@@ -535,10 +589,34 @@ bf16_reduce_kernel(Bf16Inputs io, float* reduced, long long first_value, long lo
     if (kSquares) cta_accumulate(squares, squared_sum);
 }
 
+// How an all-reduce kernel is launched.  ctas: 0 = fill the machine, n > 0 =
+// at most n CTAs.  asynchronous: 1 = cp.async rings in shared memory, 0 =
+// register prefetch.  exclusive: 1 (with asynchronous) = big CTAs that take a
+// whole SM each (see kExclusiveSharedBytes), so `ctas` is then the number of
+// SMs the collective owns while it runs.
+struct CollectiveShape {
+    int ctas;
+    int asynchronous;
+    int exclusive;
+};
+
+// The process-wide default (nntrain_gradient_configure*).
+CollectiveShape default_collective_shape();
+
+// What every group handle starts with, so one configure call serves both the
+// one-process-per-GPU group and the in-process group.
+constexpr int kKindProcessGroup = 0x47524f55;
+constexpr int kKindLocalGroup = 0x4c4f4341;
+struct GroupHeader {
+    int kind;
+    CollectiveShape shape;
+};
+
 // ---- launchers (reduce_launch.cu) --------------------------------------------
 cudaError_t launch_bfp8_reduce_reencode(const EncodedShards& shards, long long first_value,
                                         long long end_value, int block, float reduction_scale,
-                                        double* squared_sum, int* finite_status, cudaStream_t stream);
+                                        double* squared_sum, int* finite_status, cudaStream_t stream,
+                                        const CollectiveShape* shape = nullptr);
 
 cudaError_t launch_bfp8_sum_to_f32(const EncodedInputs& in, float* reduced, long long length,
                                    long long block, float reduction_scale, double* squared_sum,
@@ -546,6 +624,7 @@ cudaError_t launch_bfp8_sum_to_f32(const EncodedInputs& in, float* reduced, long
 
 cudaError_t launch_bf16_reduce(const Bf16Inputs& io, float* reduced, long long first_value,
                                long long end_value, float reduction_scale, double* squared_sum,
-                               bool square_of_bf16, cudaStream_t stream);
+                               bool square_of_bf16, cudaStream_t stream,
+                               const CollectiveShape* shape = nullptr);
 
 }  // namespace ngb

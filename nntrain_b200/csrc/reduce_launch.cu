@@ -8,12 +8,19 @@ inline bool aligned_to(const void* p, std::uintptr_t bytes) {
     return (reinterpret_cast<std::uintptr_t>(p) & (bytes - 1)) == 0;
 }
 
+int capped_grid(long long work_items, int cap_ctas, int per_sm_default) {
+    if (work_items < 1) work_items = 1;
+    long long cap = cap_ctas;
+    if (cap <= 0) cap = static_cast<long long>(sm_count()) * per_sm_default;
+    return static_cast<int>(work_items < cap ? work_items : cap);
+}
+
 template <int kBlock, int kRanks>
 cudaError_t run_reencode(const EncodedShards& shards, long long first_value, long long end_value,
                          float reduction_scale, double* squared_sum, int* finite_status,
-                         bool vector_ok, cudaStream_t stream) {
+                         bool vector_ok, const CollectiveShape& shape, cudaStream_t stream) {
     const long long tiles = (end_value - first_value + 511) / 512;
-    const int grid = collective_grid_for((tiles + kWarpsPerCta - 1) / kWarpsPerCta);
+    const int grid = capped_grid((tiles + kWarpsPerCta - 1) / kWarpsPerCta, shape.ctas, kCtasPerSmDefault);
     if (squared_sum != nullptr) {
         bfp8_reduce_reencode_kernel<kBlock, kRanks, true><<<grid, kThreads, 0, stream>>>(
             shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok);
@@ -25,31 +32,36 @@ cudaError_t run_reencode(const EncodedShards& shards, long long first_value, lon
 }
 
 // cp.async ring variant: needs 16-byte aligned arenas and a compile-time rank
-// count.  One CTA per SM when it runs beside codec kernels; alone it may use
-// as many CTAs as the ring's shared memory lets an SM hold.
-template <int kBlock, int kRanks, int kStages>
+// count.  Shared: 8 warps per CTA, one CTA per SM when it runs beside codec
+// kernels, as many as the ring's shared memory lets an SM hold when alone.
+// Exclusive (kWarps > 8 and the whole SM's shared memory): `shape.ctas` SMs
+// belong to the kernel while it runs.
+template <int kBlock, int kRanks, int kStages, int kWarps>
 cudaError_t run_reencode_async(const EncodedShards& shards, long long first_value, long long end_value,
                                float reduction_scale, double* squared_sum, int* finite_status,
-                               cudaStream_t stream) {
-    constexpr size_t bytes = reduce_ring_bytes<kRanks, kStages>();
+                               const CollectiveShape& shape, cudaStream_t stream) {
+    constexpr size_t ring_bytes = reduce_ring_bytes<kRanks, kStages, kWarps>();
+    static_assert(ring_bytes <= kExclusiveSharedBytes, "ring does not fit in one SM");
+    const size_t bytes = shape.exclusive ? kExclusiveSharedBytes : ring_bytes;
     const long long tiles = (end_value - first_value + 511) / 512;
-    const long long work = (tiles + kWarpsPerCta - 1) / kWarpsPerCta;
-    long long cap = launch_policy().collective_ctas;
-    if (cap <= 0) cap = static_cast<long long>(sm_count()) * (bytes > 100 * 1024 ? 1 : 2);
+    const long long work = (tiles + kWarps - 1) / kWarps;
+    long long cap = shape.ctas;
+    if (cap <= 0) cap = static_cast<long long>(sm_count()) * ((shape.exclusive || bytes > 100 * 1024) ? 1 : 2);
+    if (shape.exclusive && cap > sm_count()) cap = sm_count();
     const int grid = static_cast<int>(work < cap ? work : cap);
     cudaError_t e;
     if (squared_sum != nullptr) {
-        auto kernel = bfp8_reduce_reencode_async_kernel<kBlock, kRanks, true, kStages>;
+        auto kernel = bfp8_reduce_reencode_async_kernel<kBlock, kRanks, true, kStages, kWarps>;
         e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
         if (e != cudaSuccess) return e;
-        kernel<<<grid, kThreads, bytes, stream>>>(shards, first_value, end_value, reduction_scale, squared_sum,
-                                                 finite_status);
+        kernel<<<grid, kWarps * 32, bytes, stream>>>(shards, first_value, end_value, reduction_scale, squared_sum,
+                                                    finite_status);
     } else {
-        auto kernel = bfp8_reduce_reencode_async_kernel<kBlock, kRanks, false, kStages>;
+        auto kernel = bfp8_reduce_reencode_async_kernel<kBlock, kRanks, false, kStages, kWarps>;
         e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
         if (e != cudaSuccess) return e;
-        kernel<<<grid, kThreads, bytes, stream>>>(shards, first_value, end_value, reduction_scale, nullptr,
-                                                 finite_status);
+        kernel<<<grid, kWarps * 32, bytes, stream>>>(shards, first_value, end_value, reduction_scale, nullptr,
+                                                    finite_status);
     }
     return cudaPeekAtLastError();
 }
@@ -57,21 +69,35 @@ cudaError_t run_reencode_async(const EncodedShards& shards, long long first_valu
 template <int kBlock>
 cudaError_t dispatch_reencode(const EncodedShards& shards, long long first_value, long long end_value,
                               float reduction_scale, double* squared_sum, int* finite_status,
-                              bool vector_ok, cudaStream_t stream) {
-    if (vector_ok && launch_policy().collective_async) {
+                              bool vector_ok, const CollectiveShape& shape, cudaStream_t stream) {
+#define NGB_RING(R, S, W) \
+    return run_reencode_async<kBlock, R, S, W>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, shape, stream)
+    if (vector_ok && shape.asynchronous && shape.exclusive) {
+        // rings sized for an SM of their own: ~130-150 KB of loads in flight per SM
         switch (shards.inputs) {
-            case 2: return run_reencode_async<kBlock, 2, 8>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, stream);
-            case 4: return run_reencode_async<kBlock, 4, 6>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, stream);
-            case 8: return run_reencode_async<kBlock, 8, 4>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, stream);
+            case 2: NGB_RING(2, 8, 16);
+            case 4: NGB_RING(4, 5, 16);
+            case 8: NGB_RING(8, 3, 12);
             default: break;
         }
     }
-    switch (shards.inputs) {
-        case 2: return run_reencode<kBlock, 2>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, stream);
-        case 4: return run_reencode<kBlock, 4>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, stream);
-        case 8: return run_reencode<kBlock, 8>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, stream);
-        default: return run_reencode<kBlock, 0>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, stream);
+    if (vector_ok && shape.asynchronous) {
+        switch (shards.inputs) {
+            case 2: NGB_RING(2, 8, 8);
+            case 4: NGB_RING(4, 6, 8);
+            case 8: NGB_RING(8, 4, 8);
+            default: break;
+        }
     }
+#undef NGB_RING
+#define NGB_PREFETCH(R) \
+    case R: return run_reencode<kBlock, R>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, shape, stream)
+    switch (shards.inputs) {
+        NGB_PREFETCH(2); NGB_PREFETCH(3); NGB_PREFETCH(4); NGB_PREFETCH(5);
+        NGB_PREFETCH(6); NGB_PREFETCH(7); NGB_PREFETCH(8);
+        default: return run_reencode<kBlock, 0>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, shape, stream);
+    }
+#undef NGB_PREFETCH
 }
 
 template <int kShift, bool kGuard, bool kSquares, bool kMaximum>
@@ -100,9 +126,16 @@ void dispatch_sum(int grid, cudaStream_t stream, const EncodedInputs& in, float*
 
 }  // namespace
 
+CollectiveShape default_collective_shape() {
+    const LaunchPolicy policy = launch_policy();
+    return CollectiveShape{policy.collective_ctas, policy.collective_async, 0};
+}
+
 cudaError_t launch_bfp8_reduce_reencode(const EncodedShards& shards, long long first_value,
                                         long long end_value, int block, float reduction_scale,
-                                        double* squared_sum, int* finite_status, cudaStream_t stream) {
+                                        double* squared_sum, int* finite_status, cudaStream_t stream,
+                                        const CollectiveShape* shape_or_null) {
+    const CollectiveShape shape = shape_or_null ? *shape_or_null : default_collective_shape();
     if (shards.inputs < 1 || shards.inputs > kMaxRanks || shards.outputs < 1 || shards.outputs > kMaxRanks)
         return cudaErrorInvalidValue;
     if (first_value < 0 || end_value <= first_value) return cudaErrorInvalidValue;
@@ -118,9 +151,9 @@ cudaError_t launch_bfp8_reduce_reencode(const EncodedShards& shards, long long f
         vector_ok = vector_ok && aligned_to(shards.out_payload[d], 16);
     }
     switch (block) {
-        case 32: return dispatch_reencode<32>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, stream);
-        case 64: return dispatch_reencode<64>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, stream);
-        default: return dispatch_reencode<128>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, stream);
+        case 32: return dispatch_reencode<32>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, shape, stream);
+        case 64: return dispatch_reencode<64>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, shape, stream);
+        default: return dispatch_reencode<128>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, vector_ok, shape, stream);
     }
 }
 
@@ -142,9 +175,22 @@ cudaError_t launch_bfp8_sum_to_f32(const EncodedInputs& in, float* reduced, long
     return cudaPeekAtLastError();
 }
 
+template <int kRanks>
+void run_bf16_reduce(int grid, cudaStream_t stream, const Bf16Inputs& io, float* reduced, long long first_value,
+                     long long end_value, float reduction_scale, double* squared_sum, bool square_of_bf16,
+                     bool vector_ok) {
+    if (!squared_sum)
+        bf16_reduce_kernel<kRanks, false, false><<<grid, kThreads, 0, stream>>>(io, reduced, first_value, end_value, reduction_scale, nullptr, vector_ok);
+    else if (square_of_bf16)
+        bf16_reduce_kernel<kRanks, true, true><<<grid, kThreads, 0, stream>>>(io, reduced, first_value, end_value, reduction_scale, squared_sum, vector_ok);
+    else
+        bf16_reduce_kernel<kRanks, true, false><<<grid, kThreads, 0, stream>>>(io, reduced, first_value, end_value, reduction_scale, squared_sum, vector_ok);
+}
+
 cudaError_t launch_bf16_reduce(const Bf16Inputs& io, float* reduced, long long first_value,
                                long long end_value, float reduction_scale, double* squared_sum,
-                               bool square_of_bf16, cudaStream_t stream) {
+                               bool square_of_bf16, cudaStream_t stream, const CollectiveShape* shape_or_null) {
+    const CollectiveShape shape = shape_or_null ? *shape_or_null : default_collective_shape();
     if (io.inputs < 1 || io.inputs > kMaxRanks || io.outputs < 0 || io.outputs > kMaxRanks)
         return cudaErrorInvalidValue;
     if (first_value < 0 || end_value <= first_value || (!reduced && io.outputs == 0 && !squared_sum))
@@ -159,13 +205,14 @@ cudaError_t launch_bf16_reduce(const Bf16Inputs& io, float* reduced, long long f
         vector_ok = vector_ok && aligned_to(io.out_bf16[d], 16);
     }
     const long long groups = (end_value - first_value + 7) / 8;
-    const int grid = collective_grid_for((groups + kThreads - 1) / kThreads);
-    if (!squared_sum)
-        bf16_reduce_kernel<false, false><<<grid, kThreads, 0, stream>>>(io, reduced, first_value, end_value, reduction_scale, nullptr, vector_ok);
-    else if (square_of_bf16)
-        bf16_reduce_kernel<true, true><<<grid, kThreads, 0, stream>>>(io, reduced, first_value, end_value, reduction_scale, squared_sum, vector_ok);
-    else
-        bf16_reduce_kernel<true, false><<<grid, kThreads, 0, stream>>>(io, reduced, first_value, end_value, reduction_scale, squared_sum, vector_ok);
+    const int grid = capped_grid((groups + kThreads - 1) / kThreads, shape.ctas, kCtasPerSmDefault);
+#define NGB_BF16(R) \
+    case R: run_bf16_reduce<R>(grid, stream, io, reduced, first_value, end_value, reduction_scale, squared_sum, square_of_bf16, vector_ok); break
+    switch (io.inputs) {
+        NGB_BF16(2); NGB_BF16(3); NGB_BF16(4); NGB_BF16(5); NGB_BF16(6); NGB_BF16(7); NGB_BF16(8);
+        default: run_bf16_reduce<0>(grid, stream, io, reduced, first_value, end_value, reduction_scale, squared_sum, square_of_bf16, vector_ok); break;
+    }
+#undef NGB_BF16
     return cudaPeekAtLastError();
 }
 

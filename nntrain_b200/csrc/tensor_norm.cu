@@ -97,7 +97,12 @@ bfp8_squared_sum_kernel(const signed char* __restrict__ payload, const float* __
 }
 
 __global__ void __launch_bounds__(kThreads)
-f32_scale_kernel(float* values, long long length, float multiplier, bool vector_ok) {
+f32_scale_kernel(float* values, long long length, float multiplier, const float* coefficient, bool vector_ok) {
+    // with a device-resident coefficient nothing is touched when it is 1
+    if (coefficient != nullptr) {
+        multiplier = coefficient[1];
+        if (multiplier == 1.0f) return;
+    }
     const long long thread = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
     const long long threads = static_cast<long long>(gridDim.x) * kThreads;
     const long long vectors = vector_ok ? length / 4 : 0;
@@ -113,7 +118,12 @@ f32_scale_kernel(float* values, long long length, float multiplier, bool vector_
 
 // g = bf16_rn(f32(g) * multiplier)  (pure_bfloat16_gradients.cu:337-348)
 __global__ void __launch_bounds__(kThreads)
-bf16_scale_kernel(unsigned short* values, long long length, float multiplier, bool vector_ok) {
+bf16_scale_kernel(unsigned short* values, long long length, float multiplier, const float* coefficient,
+                  bool vector_ok) {
+    if (coefficient != nullptr) {
+        multiplier = coefficient[1];
+        if (multiplier == 1.0f) return;
+    }
     const long long thread = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
     const long long threads = static_cast<long long>(gridDim.x) * kThreads;
     const long long groups = vector_ok ? length / 8 : 0;
@@ -230,15 +240,17 @@ cudaError_t launch_bfp8_squared_sum(const signed char* payload, const float* sca
     return cudaPeekAtLastError();
 }
 
-cudaError_t launch_f32_scale(float* values, long long length, float multiplier, cudaStream_t stream) {
+cudaError_t launch_f32_scale(float* values, long long length, float multiplier, cudaStream_t stream,
+                             const float* coefficient) {
     f32_scale_kernel<<<elementwise_grid(length / 4 + 1), kThreads, 0, stream>>>(
-        values, length, multiplier, aligned_to(values, 16));
+        values, length, multiplier, coefficient, aligned_to(values, 16));
     return cudaPeekAtLastError();
 }
 
-cudaError_t launch_bf16_scale(unsigned short* values, long long length, float multiplier, cudaStream_t stream) {
+cudaError_t launch_bf16_scale(unsigned short* values, long long length, float multiplier, cudaStream_t stream,
+                              const float* coefficient) {
     bf16_scale_kernel<<<elementwise_grid(length / 8 + 1), kThreads, 0, stream>>>(
-        values, length, multiplier, aligned_to(values, 16));
+        values, length, multiplier, coefficient, aligned_to(values, 16));
     return cudaPeekAtLastError();
 }
 
@@ -345,17 +357,17 @@ NNTRAIN_EXPORT int nntrain_gradient_clip_coefficient(int device, const double* s
 // Applies a clip multiplier to a whole arena.  kind 0: fp32 values *= c;
 // kind 1: bf16 values = bf16_rn(f32 * c); kind 2: BFP8 scale sidecar
 // scales[i] = fmaxf(scales[i] * c, FLT_MIN), payload untouched.  When
-// `coefficient` is non-null the multiplier is coefficient[1] on the device
-// (kind 2 only) and `multiplier` is ignored.
+// `coefficient` is non-null the multiplier is coefficient[1] read on the
+// device (the output of nntrain_gradient_clip_coefficient), `multiplier` is
+// ignored, and a coefficient of exactly 1 leaves the arena untouched.
 NNTRAIN_EXPORT int nntrain_gradient_clip_apply(int device, int kind, void* values, long long count,
                                                float multiplier, const float* coefficient, cudaStream_t stream) {
     if (!values || count <= 0 || kind < 0 || kind > 2) return static_cast<int>(cudaErrorInvalidValue);
     if (!coefficient && (!std::isfinite(multiplier) || !(multiplier > 0.0f)))
         return static_cast<int>(cudaErrorInvalidValue);
-    if (coefficient && kind != 2) return static_cast<int>(cudaErrorInvalidValue);
     int status = select_device(device);
     if (status != cudaSuccess) return status;
-    if (kind == 0) return static_cast<int>(launch_f32_scale(static_cast<float*>(values), count, multiplier, stream));
-    if (kind == 1) return static_cast<int>(launch_bf16_scale(static_cast<unsigned short*>(values), count, multiplier, stream));
+    if (kind == 0) return static_cast<int>(launch_f32_scale(static_cast<float*>(values), count, multiplier, stream, coefficient));
+    if (kind == 1) return static_cast<int>(launch_bf16_scale(static_cast<unsigned short*>(values), count, multiplier, stream, coefficient));
     return static_cast<int>(launch_bfp8_scale_scales(static_cast<float*>(values), count, multiplier, coefficient, stream));
 }

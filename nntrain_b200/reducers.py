@@ -99,8 +99,19 @@ class GradientGroup:
             identifier, world, rank, device, ctypes.addressof(handle)))
         self.handle = handle.value
 
+    def configure(self, collective_ctas: int = 0, asynchronous_copies: bool = True, exclusive_sms: bool = False):
+        """Launch shape of THIS group's all-reduce kernels (other groups in the
+        process keep theirs)."""
+        check("gradient_group_configure", load().nntrain_gradient_group_configure(
+            self.handle, collective_ctas, int(asynchronous_copies), int(exclusive_sms)))
+
     def poll(self) -> int:
+        """0 while the communicator is healthy; never blocks."""
         return load().nntrain_gradient_group_poll(self.handle)
+
+    def abort(self) -> None:
+        """Gives the communicator up without waiting (a peer was declared lost)."""
+        check("gradient_group_abort", load().nntrain_gradient_group_abort(self.handle))
 
     def sum(self, values: torch.Tensor, stream=None) -> None:
         check("gradient_group_sum", load().nntrain_gradient_group_sum(
@@ -189,6 +200,38 @@ class StepResult:
     coefficient: float     # clip multiplier that was applied (1.0 = none)
     squared_sum: float
     finite: bool
+    # True when the fp32 arena holds the clipped gradient too.  The clip is
+    # scale-only: payload x clipped scales is the authoritative gradient after a
+    # step (the reference marks the BFP8 buffers synchronized and drops the fp32
+    # copy, NNtrain.Core/Tensors/Tensor.CudaKernels.cs:321-437); the fp32 arena
+    # keeps the decode of the UNCLIPPED result unless the reducer was built with
+    # clip_fp32=True or the coefficient is 1.
+    fp32_clipped: bool = True
+
+
+class _ResultBlock:
+    """The 16 bytes a step leaves for the host: sum of squares (double), finite
+    flag (int32), applied clip coefficient (float32).  One device buffer, read
+    back with ONE copy (the reference's transfer budget per step is the finite
+    flags plus one double, NNtrain.Core.Tests/CudaBfp8GradientReducerTests.cs:39-41)."""
+
+    def __init__(self, device: int):
+        with torch.cuda.device(device):
+            self.raw = torch.zeros(16, dtype=torch.uint8, device=f"cuda:{device}")
+            self.norm_and_coefficient = torch.zeros(2, dtype=torch.float32, device=f"cuda:{device}")
+        self.squared_sum = self.raw[0:8].view(torch.float64)
+        self.finite_status = self.raw[8:12].view(torch.int32)
+        self.coefficient = self.raw[12:16].view(torch.float32)
+
+    def read(self, clipped: bool) -> tuple[float, bool, float, float]:
+        """(squared_sum, finite, norm, coefficient) from one 16-byte read."""
+        import numpy as np
+        host = self.raw.cpu().numpy()
+        squared_sum = float(host[0:8].view(np.float64)[0])
+        finite = int(host[8:12].view(np.int32)[0]) == 0
+        coefficient = float(host[12:16].view(np.float32)[0]) if clipped else 1.0
+        norm = float(np.float32(np.sqrt(np.float64(squared_sum))))   # what the device computed: (float)sqrt(double)
+        return squared_sum, finite, norm, coefficient
 
 
 class Bfp8ArenaAllReduce:
@@ -214,11 +257,12 @@ class Bfp8ArenaAllReduce:
                  chunk_elements: int | None = None, reduction_scale: float = 1.0,
                  write_fp32: bool = True, codec_iterations_per_cta: int | None = None,
                  collective_ctas: int | None = None, chunk_plan: list[int] | None = None,
-                 collective_async: int | None = None):
+                 collective_async: int | None = None, collective_exclusive: bool | None = None,
+                 clip_fp32: bool = False):
         if block_size not in (32, 64, 128):
             raise ValueError("block size must be 32, 64 or 128")
         self.group, self.elements, self.block, self.mode = group, elements, block_size, mode
-        self.reduction_scale, self.write_fp32 = reduction_scale, write_fp32
+        self.reduction_scale, self.write_fp32, self.clip_fp32 = reduction_scale, write_fp32, clip_fp32
         world = group.world
         align = 512 * world
         if chunk_elements is None or chunk_elements >= elements:
@@ -229,9 +273,6 @@ class Bfp8ArenaAllReduce:
         # short first chunk (the wire starts early), long middle chunks (few
         # barriers) and a short last one (little decode left at the end).
         if chunk_plan is None and chunk_elements == elements and world > 1 and elements >= (64 << 20):
-            # default for a large arena: short first chunk (the wire starts
-            # early), long middle chunks (few barriers), short last chunks
-            # (little decode left when the wire is done)
             chunk_plan = [int(elements * f) for f in (0.03, 0.10, 0.26, 0.26, 0.20, 0.09)]
         if chunk_plan:
             plan = [max(align, int(c) // align * align) for c in chunk_plan]
@@ -255,9 +296,9 @@ class Bfp8ArenaAllReduce:
             self.scales_buffer = PeerBuffer(group, self.scale_count * 4)
             self.payload = self.payload_buffer.tensor(torch.int8, elements)
             self.scales = self.scales_buffer.tensor(torch.float32, self.scale_count)
-            self.squared_sum = torch.zeros(1, dtype=torch.float64, device=f"cuda:{device}")
-            self.finite_status = torch.zeros(1, dtype=torch.int32, device=f"cuda:{device}")
-            self.norm_and_coefficient = torch.zeros(2, dtype=torch.float32, device=f"cuda:{device}")
+            self.result = _ResultBlock(device)
+            self.squared_sum, self.finite_status = self.result.squared_sum, self.result.finite_status
+            self.norm_and_coefficient = self.result.norm_and_coefficient
             self.staging_payload = self.staging_scales = None
             if mode != PEER and world > 1:
                 first, end = shard_range(min(self.chunk, elements), world, 0)
@@ -266,24 +307,30 @@ class Bfp8ArenaAllReduce:
                 self.staging_payload = torch.empty(world * shard, dtype=torch.int8, device=f"cuda:{device}")
                 self.staging_scales = torch.empty(world * shard // block_size + world, dtype=torch.float32,
                                                   device=f"cuda:{device}")
-            # Overlap shape: with more than one chunk in flight the codec kernels
-            # use short-lived CTAs and the all-reduce kernel a capped grid on a
-            # high-priority stream, so the three stages share the SMs.
+            # Overlap shape: with more than one chunk in flight the all-reduce
+            # kernel runs on a high-priority stream beside the encode / decode
+            # kernels of the neighbouring chunks.  The shape belongs to the
+            # group, not to the process, so another reducer keeps its own.
             overlapped = world > 1 and len(self.spans) > 1
-            if codec_iterations_per_cta is None:
-                codec_iterations_per_cta = 2
-            if collective_ctas is None:
-                # (with the copy-engine transport the owner kernel is local and short: no cap)
-                capped = overlapped and mode == PEER
-                collective_ctas = torch.cuda.get_device_properties(device).multi_processor_count if capped else 0
-            self.codec_iterations_per_cta, self.collective_ctas = codec_iterations_per_cta, collective_ctas
-            check("gradient_configure", load().nntrain_gradient_configure(codec_iterations_per_cta, collective_ctas))
-            # Measured on 8 x B200: beside codec kernels the register-prefetch
-            # kernel does better; alone, the cp.async ring does.
+            sms = torch.cuda.get_device_properties(device).multi_processor_count
+            if collective_exclusive is None:
+                collective_exclusive = False
             if collective_async is None:
-                collective_async = 0 if overlapped else 1
-            self.collective_async = collective_async
-            check("gradient_configure_collective", load().nntrain_gradient_configure_collective(collective_async))
+                # beside codec kernels the register-prefetch kernel did better
+                # than the shared cp.async ring; alone, the ring did
+                collective_async = 1 if (collective_exclusive or not overlapped) else 0
+            if collective_ctas is None:
+                collective_ctas = sms if (overlapped and mode == PEER and not collective_exclusive) else 0
+                if collective_exclusive:
+                    collective_ctas = (sms * 3) // 8
+            self.collective_ctas, self.collective_async = collective_ctas, collective_async
+            self.collective_exclusive = bool(collective_exclusive)
+            if world > 1:
+                group.configure(collective_ctas, bool(collective_async), bool(collective_exclusive))
+            self.codec_iterations_per_cta = codec_iterations_per_cta
+            if codec_iterations_per_cta is not None:
+                # the encode / decode grids have no group: this one is process-wide
+                check("gradient_configure", load().nntrain_gradient_configure(codec_iterations_per_cta, 0))
             self.compute_stream = torch.cuda.Stream(device)
             self.communication_stream = torch.cuda.Stream(device, priority=-1)
             self.decode_stream = torch.cuda.Stream(device)
@@ -297,6 +344,7 @@ class Bfp8ArenaAllReduce:
             self.reduced = [torch.cuda.Event() for _ in range(chunks)]
             self.uploaded = [torch.cuda.Event() for _ in range(chunks)]
         self.kernel_launches = 0
+        self._clipped = False
 
     @property
     def transport_bytes_per_step(self) -> int:
@@ -319,12 +367,11 @@ class Bfp8ArenaAllReduce:
         group, device, lib = self.group, self.group.device, load()
         world = group.world
         current = torch.cuda.current_stream(device)
-        self.squared_sum.zero_()
-        self.finite_status.zero_()
+        self.result.raw.zero_()
         ready = current.record_event()
         for stream in (self.compute_stream, self.communication_stream, self.h2d_stream, self.d2h_stream):
             stream.wait_event(ready)
-        launches = 2
+        launches = 0      # the library's own kernels (torch's 16-byte fill and copy are not counted)
         spans = self.spans
         first_stream = self.communication_stream if world == 1 else self.compute_stream
         for index, (start, stop) in enumerate(spans):
@@ -372,6 +419,7 @@ class Bfp8ArenaAllReduce:
         # The decodes read the scale sidecar as reduced; the clip rewrites it in
         # place, so it must not start before the last decode has finished.
         self.communication_stream.wait_stream(self.decode_stream)
+        self._clipped = max_norm is not None
         with torch.cuda.stream(self.communication_stream):
             if max_norm is not None:
                 GradientNorm.clip_coefficient(device, self.squared_sum, max_norm, self.norm_and_coefficient,
@@ -379,6 +427,13 @@ class Bfp8ArenaAllReduce:
                 GradientNorm.clip_apply(device, GradientNorm.BFP8, self.scales,
                                         coefficient=self.norm_and_coefficient, stream=self.communication_stream)
                 launches += 2
+                if self.clip_fp32 and self.write_fp32:
+                    # an extra pass over the fp32 arena (8 B/value, skipped on
+                    # the device when the coefficient is 1)
+                    GradientNorm.clip_apply(device, GradientNorm.FP32, gradient,
+                                            coefficient=self.norm_and_coefficient, stream=self.communication_stream)
+                    launches += 1
+                self.result.coefficient.copy_(self.norm_and_coefficient[1:2])
             if host_scales is not None:
                 host_scales.copy_(self.scales, non_blocking=True)
         self.communication_stream.wait_stream(self.decode_stream)
@@ -415,19 +470,15 @@ class Bfp8ArenaAllReduce:
         return 1
 
     def complete(self, max_norm: float | None = None) -> StepResult:
-        """The step's only device-to-host read: sum of squares, finite flag and
-        (when clipping) norm + coefficient, 24 bytes."""
+        """The step's only device-to-host read: 16 bytes (sum of squares,
+        finite flag, applied clip coefficient) in one copy."""
         device = self.group.device
         torch.cuda.current_stream(device).synchronize()
-        squared_sum = float(self.squared_sum.item())
-        finite = int(self.finite_status.item()) == 0
-        if max_norm is not None:
-            norm, coefficient = (float(v) for v in self.norm_and_coefficient.tolist())
-        else:
-            norm, coefficient = float(torch.tensor(squared_sum, dtype=torch.float64).sqrt().float()), 1.0
+        squared_sum, finite, norm, coefficient = self.result.read(self._clipped and max_norm is not None)
         if not finite:
             raise FloatingPointError("BFP8 gradient reduction saw a non-finite gradient")
-        return StepResult(norm, coefficient, squared_sum, finite)
+        return StepResult(norm, coefficient, squared_sum, finite,
+                          fp32_clipped=(coefficient == 1.0 or (self.clip_fp32 and self.write_fp32)))
 
     def close(self) -> None:
         torch.cuda.synchronize(self.group.device)
@@ -470,7 +521,6 @@ class Bf16ArenaAllReduce:
                 first, end = shard_range(chunk_elements, world, 0)
                 shard = (end - first + 511) // 512 * 512
                 self.staging = torch.empty(world * shard, dtype=torch.int16, device=f"cuda:{device}")
-        check("gradient_configure", load().nntrain_gradient_configure(2, 0))
 
     @property
     def transport_bytes_per_step(self) -> int:
@@ -509,3 +559,292 @@ class Bf16ArenaAllReduce:
         torch.cuda.synchronize(self.group.device)
         self.values = None
         self.buffer.close()
+
+
+# ---- one process, all devices -------------------------------------------------------
+class LocalGradientGroup:
+    """The ranks of a job that ONE process drives (the reference engine's host
+    model: one worker thread per device, NNtrain.Core/Training/
+    CudaReplicaExecutor.cs:29-116,339-369).  `devices[r]` is rank r's device; a
+    device may repeat, in which case those ranks share it (the way the N-rank
+    path is exercised on a single GPU)."""
+
+    def __init__(self, devices):
+        self.devices = list(devices)
+        self.world = len(self.devices)
+        handle = ctypes.c_void_p()
+        check("gradient_local_group_create", load().nntrain_gradient_local_group_create(
+            self.world, (ctypes.c_int * self.world)(*self.devices), ctypes.addressof(handle)))
+        self.handle = handle.value
+
+    def configure(self, collective_ctas: int = 0, asynchronous_copies: bool = True, exclusive_sms: bool = False):
+        check("gradient_group_configure", load().nntrain_gradient_group_configure(
+            self.handle, collective_ctas, int(asynchronous_copies), int(exclusive_sms)))
+
+    def allreduce_bfp8(self, payload_pointers, scales_pointers, length: int, block_size: int,
+                       reduction_scale: float, squared_sum_pointers, finite_status_pointers, phase: int,
+                       streams) -> None:
+        check("gradient_local_allreduce_bfp8", load().nntrain_gradient_local_allreduce_bfp8(
+            self.handle, _pointer_table(payload_pointers), _pointer_table(scales_pointers), length, block_size,
+            reduction_scale, _pointer_table(squared_sum_pointers) if squared_sum_pointers else None,
+            _pointer_table(finite_status_pointers) if finite_status_pointers else None, phase,
+            _pointer_table(streams)))
+
+    def allreduce_bf16(self, value_pointers, length: int, reduction_scale: float, squared_sum_pointers,
+                       phase: int, streams) -> None:
+        check("gradient_local_allreduce_bf16", load().nntrain_gradient_local_allreduce_bf16(
+            self.handle, _pointer_table(value_pointers), length, reduction_scale,
+            _pointer_table(squared_sum_pointers) if squared_sum_pointers else None, phase,
+            _pointer_table(streams)))
+
+    def close(self) -> None:
+        if self.handle:
+            check("gradient_local_group_destroy", load().nntrain_gradient_local_group_destroy(self.handle))
+            self.handle = None
+
+
+class _RankState:
+    """What one rank of an in-process reducer owns on its device."""
+
+    def __init__(self, device: int, elements: int, scale_count: int, chunks: int):
+        self.device = device
+        with torch.cuda.device(device):
+            name = f"cuda:{device}"
+            self.payload = torch.empty(elements, dtype=torch.int8, device=name)
+            self.scales = torch.empty(scale_count, dtype=torch.float32, device=name)
+            self.result = _ResultBlock(device)
+            self.compute_stream = torch.cuda.Stream(device)
+            self.communication_stream = torch.cuda.Stream(device, priority=-1)
+            self.decode_stream = torch.cuda.Stream(device)
+        self.begun = CudaGradientBuckets.create_ready_event(device)
+        self.encoded = [CudaGradientBuckets.create_ready_event(device) for _ in range(chunks)]
+        self.reduced = [CudaGradientBuckets.create_ready_event(device) for _ in range(chunks)]
+        self.decoded = CudaGradientBuckets.create_ready_event(device)
+        self.done = CudaGradientBuckets.create_ready_event(device)
+        self.gradient = None
+
+    def events(self):
+        return [self.begun, self.decoded, self.done, *self.encoded, *self.reduced]
+
+
+def _wait(stream, event) -> None:
+    check("gradient_stream_wait_event", load().nntrain_gradient_stream_wait_event(_stream(stream), event))
+
+
+class InProcessBfp8AllReduce:
+    """`Bfp8ArenaAllReduce` for ranks that live in one process.
+
+    The flow is the reference plan's (NNtrain.Core/Training/
+    CudaBfp8GradientAllReduce.cs:225-364): every device's worker thread calls
+    `publish(rank, gradient)` once its backward is enqueued -- that encodes the
+    rank's arena on the rank's own streams -- and the worker that arrives LAST
+    enqueues the cross-device all-reduce, the decodes and the clip for all ranks
+    (`publish` returns True for it).  `complete()` then reads 16 bytes per rank.
+    Ranks are ordered by events only, so a single thread may drive every rank
+    (`enqueue`)."""
+
+    def __init__(self, group: LocalGradientGroup, elements: int, block_size: int = 32,
+                 chunk_elements: int | None = None, reduction_scale: float = 1.0, write_fp32: bool = True):
+        import threading
+        if block_size not in (32, 64, 128):
+            raise ValueError("block size must be 32, 64 or 128")
+        self.group, self.elements, self.block = group, elements, block_size
+        self.reduction_scale, self.write_fp32 = reduction_scale, write_fp32
+        world = group.world
+        align = 512 * world
+        if chunk_elements is None or chunk_elements >= elements:
+            chunk_elements = elements
+        else:
+            chunk_elements = max(align, chunk_elements // align * align)
+        self.spans = [(a, min(a + chunk_elements, elements)) for a in range(0, elements, chunk_elements)]
+        self.scale_count = (elements + block_size - 1) // block_size
+        self.ranks = [_RankState(d, elements, self.scale_count, len(self.spans)) for d in group.devices]
+        self._lock = threading.Lock()
+        self._arrived = 0
+        self._max_norm = None
+        self._clipped = False
+        self.kernel_launches = 0
+
+    @property
+    def transport_bytes_per_step(self) -> int:
+        world = self.group.world
+        return 2 * (world - 1) * (self.elements + 4 * self.scale_count) // world
+
+    def _slices(self, state: _RankState, start: int, stop: int):
+        return (state.payload[start:stop],
+                state.scales[start // self.block:(stop + self.block - 1) // self.block])
+
+    def publish(self, rank: int, gradient: torch.Tensor, max_norm: float | None = None) -> bool:
+        """Rank `rank`'s part of a step, called on that rank's worker thread (or
+        by a single driver): encode the arena behind the work already on the
+        rank's current stream.  Returns True when this call was the last
+        arrival and therefore enqueued the cross-device part."""
+        state = self.ranks[rank]
+        device = state.device
+        with torch.cuda.device(device):
+            current = torch.cuda.current_stream(device)
+            CudaGradientBuckets.record_ready(device, state.begun, current)
+            for stream in (state.compute_stream, state.communication_stream):
+                _wait(stream, state.begun)
+            # the previous step's last writers of the result block and readers of
+            # the arena (never recorded yet on the first step: no wait then)
+            _wait(state.compute_stream, state.done)
+            with torch.cuda.stream(state.compute_stream):
+                state.result.raw.zero_()
+            state.gradient = gradient
+            for index, (start, stop) in enumerate(self.spans):
+                payload, scales = self._slices(state, start, stop)
+                CudaBfp8Native.block_encode(device, gradient[start:stop], payload, scales, self.block,
+                                            finite_status=state.result.finite_status, stream=state.compute_stream)
+                CudaGradientBuckets.record_ready(device, state.encoded[index], state.compute_stream)
+        with self._lock:
+            self._arrived += 1
+            if max_norm is not None:
+                self._max_norm = max_norm
+            last = self._arrived == self.group.world
+            if last:
+                self._arrived = 0
+                max_norm, self._max_norm = self._max_norm, None
+        if last:
+            self._enqueue_collective(max_norm)
+        return last
+
+    def _enqueue_collective(self, max_norm) -> None:
+        world = self.group.world
+        launches = world * len(self.spans)           # the encodes
+        streams = [s.communication_stream.cuda_stream for s in self.ranks]
+        for index, (start, stop) in enumerate(self.spans):
+            for state in self.ranks:
+                _wait(state.communication_stream, state.encoded[index])
+            phase = (1 if index == 0 else 0) | (2 if index == len(self.spans) - 1 else 0)
+            self.group.allreduce_bfp8(
+                [s.payload.data_ptr() + start for s in self.ranks],
+                [s.scales.data_ptr() + 4 * (start // self.block) for s in self.ranks],
+                stop - start, self.block, self.reduction_scale,
+                [s.result.squared_sum.data_ptr() for s in self.ranks],
+                [s.result.finite_status.data_ptr() for s in self.ranks], phase, streams)
+            launches += world * (1 + (1 if phase & 1 else 0) + (2 if phase & 2 else 0))
+            if self.write_fp32:
+                for state in self.ranks:
+                    CudaGradientBuckets.record_ready(state.device, state.reduced[index], state.communication_stream)
+                    _wait(state.decode_stream, state.reduced[index])
+                    payload, scales = self._slices(state, start, stop)
+                    CudaBfp8Native.block_decode(state.device, payload, scales, state.gradient[start:stop],
+                                                self.block, stream=state.decode_stream)
+                    launches += 1
+        self._clipped = max_norm is not None
+        for state in self.ranks:
+            device = state.device
+            with torch.cuda.device(device):
+                # the clip rewrites the scales the decodes read
+                CudaGradientBuckets.record_ready(device, state.decoded, state.decode_stream)
+                _wait(state.communication_stream, state.decoded)
+                if max_norm is not None:
+                    block = state.result
+                    GradientNorm.clip_coefficient(device, block.squared_sum, max_norm, block.norm_and_coefficient,
+                                                  stream=state.communication_stream)
+                    GradientNorm.clip_apply(device, GradientNorm.BFP8, state.scales,
+                                            coefficient=block.norm_and_coefficient,
+                                            stream=state.communication_stream)
+                    with torch.cuda.stream(state.communication_stream):
+                        block.coefficient.copy_(block.norm_and_coefficient[1:2])
+                    launches += 2
+                CudaGradientBuckets.record_ready(device, state.done, state.communication_stream)
+        self.kernel_launches = launches
+
+    def enqueue(self, gradients, max_norm: float | None = None) -> None:
+        """Single-threaded driver: every rank's publish in turn."""
+        for rank, gradient in enumerate(gradients):
+            self.publish(rank, gradient, max_norm)
+
+    def wait(self, rank: int) -> None:
+        """Makes rank `rank`'s current stream wait for the step's result."""
+        state = self.ranks[rank]
+        with torch.cuda.device(state.device):
+            _wait(torch.cuda.current_stream(state.device), state.done)
+
+    def complete(self, max_norm: float | None = None) -> list[StepResult]:
+        """One 16-byte read per rank; the results are identical on all ranks."""
+        results, bad = [], False
+        for state in self.ranks:
+            with torch.cuda.device(state.device):
+                state.communication_stream.synchronize()
+                squared_sum, finite, norm, coefficient = state.result.read(self._clipped and max_norm is not None)
+            bad = bad or not finite
+            results.append(StepResult(norm, coefficient, squared_sum, finite, fp32_clipped=coefficient == 1.0))
+        if bad:
+            raise FloatingPointError("BFP8 gradient reduction saw a non-finite gradient")
+        return results
+
+    def close(self) -> None:
+        for state in self.ranks:
+            with torch.cuda.device(state.device):
+                torch.cuda.synchronize(state.device)
+            for event in state.events():
+                CudaGradientBuckets.destroy_event(state.device, event)
+        self.ranks = []
+
+
+class InProcessBf16AllReduce:
+    """The bf16 arena reducer for ranks that live in one process (see
+    `Bf16ArenaAllReduce` for the arithmetic and the reference lines)."""
+
+    def __init__(self, group: LocalGradientGroup, elements: int, reduction_scale: float = 1.0,
+                 chunk_elements: int | None = None):
+        self.group, self.elements, self.reduction_scale = group, elements, reduction_scale
+        world = group.world
+        align = 512 * world
+        if chunk_elements is None or chunk_elements >= elements:
+            chunk_elements = elements
+        else:
+            chunk_elements = max(align, chunk_elements // align * align)
+        self.spans = [(a, min(a + chunk_elements, elements)) for a in range(0, elements, chunk_elements)]
+        self.values, self.squared_sums, self.streams = [], [], []
+        for device in group.devices:
+            with torch.cuda.device(device):
+                self.values.append(torch.zeros(elements, dtype=torch.int16, device=f"cuda:{device}"))
+                self.squared_sums.append(torch.zeros(1, dtype=torch.float64, device=f"cuda:{device}"))
+                self.streams.append(torch.cuda.Stream(device, priority=-1))
+        self.begun = [CudaGradientBuckets.create_ready_event(d) for d in group.devices]
+
+    @property
+    def transport_bytes_per_step(self) -> int:
+        world = self.group.world
+        return 2 * (world - 1) * 2 * self.elements // world
+
+    def enqueue(self) -> None:
+        for rank, device in enumerate(self.group.devices):
+            with torch.cuda.device(device):
+                CudaGradientBuckets.record_ready(device, self.begun[rank], torch.cuda.current_stream(device))
+                _wait(self.streams[rank], self.begun[rank])
+                with torch.cuda.stream(self.streams[rank]):
+                    self.squared_sums[rank].zero_()
+        streams = [s.cuda_stream for s in self.streams]
+        for index, (start, stop) in enumerate(self.spans):
+            phase = (1 if index == 0 else 0) | (2 if index == len(self.spans) - 1 else 0)
+            self.group.allreduce_bf16([v.data_ptr() + 2 * start for v in self.values], stop - start,
+                                      self.reduction_scale, [q.data_ptr() for q in self.squared_sums], phase,
+                                      streams)
+
+    def complete(self, max_norm: float | None = None) -> list[StepResult]:
+        from .host_plan import clip_decision
+        results = []
+        for rank, device in enumerate(self.group.devices):
+            with torch.cuda.device(device):
+                self.streams[rank].synchronize()
+                squared_sum = float(self.squared_sums[rank].item())
+                if squared_sum != squared_sum or squared_sum == float("inf"):
+                    raise FloatingPointError("BF16 gradient reduction saw a non-finite gradient")
+                norm, coefficient = clip_decision(squared_sum, max_norm if max_norm is not None else 3.0e38)
+                if max_norm is not None and coefficient != 1.0:
+                    GradientNorm.clip_apply(device, GradientNorm.BF16, self.values[rank], multiplier=coefficient,
+                                            stream=self.streams[rank])
+                    self.streams[rank].synchronize()
+            results.append(StepResult(norm, coefficient, squared_sum, True))
+        return results
+
+    def close(self) -> None:
+        for rank, device in enumerate(self.group.devices):
+            torch.cuda.synchronize(device)
+            CudaGradientBuckets.destroy_event(device, self.begun[rank])
+        self.values = []

@@ -73,8 +73,8 @@ int nntrain_cuda_use_external_stream(void* stream);
 int nntrain_gradient_configure(int codec_iterations_per_cta, int collective_ctas);
 /* ABI minor 36; no counterpart in the reference.  How the owner / all-reduce
  * kernels fetch their inputs when no group says otherwise: 1 (default) =
- * cp.async rings in shared memory, 0 = register prefetch.  Same results
- * either way. */
+ * cp.async rings in shared memory, 0 = register prefetch, 2 = cp.async rings
+ * in CTAs that take a whole SM each.  Same results either way. */
 int nntrain_gradient_configure_collective(int asynchronous_copies);
 /* ABI minor 36; no counterpart in the reference.  Most CTAs a persistent
  * encode / decode grid may use (only with codec_iterations_per_cta == 0);

@@ -128,7 +128,8 @@ void dispatch_sum(int grid, cudaStream_t stream, const EncodedInputs& in, float*
 
 CollectiveShape default_collective_shape() {
     const LaunchPolicy policy = launch_policy();
-    return CollectiveShape{policy.collective_ctas, policy.collective_async, 0};
+    return CollectiveShape{policy.collective_ctas, policy.collective_async != 0 ? 1 : 0,
+                           policy.collective_async == 2 ? 1 : 0};
 }
 
 cudaError_t launch_bfp8_reduce_reencode(const EncodedShards& shards, long long first_value,

@@ -345,6 +345,10 @@ class Bfp8ArenaAllReduce:
             self.uploaded = [torch.cuda.Event() for _ in range(chunks)]
         self.kernel_launches = 0
         self._clipped = False
+        # optional: the span of the communication stream's collective work inside
+        # one step (first leading barrier .. last fence), for reporting
+        self.collective_begin = torch.cuda.Event(enable_timing=True)
+        self.collective_end = torch.cuda.Event(enable_timing=True)
 
     @property
     def transport_bytes_per_step(self) -> int:
@@ -400,6 +404,8 @@ class Bfp8ArenaAllReduce:
             scales_table = _pointer_table([p + 4 * (start // self.block) for p in self.scales_buffer.pointers])
             last = index == len(spans) - 1
             phase = (1 if index == 0 else 0) | (2 if last else 0)
+            if index == 0:
+                self.collective_begin.record(self.communication_stream)
             # A chunk's result is complete on every rank only after the NEXT
             # collective on the group: this call records final_events[index - 1]
             # right behind its leading barrier.
@@ -411,6 +417,8 @@ class Bfp8ArenaAllReduce:
                 self.final_events[index - 1] if index > 0 else None,
                 self.communication_stream.cuda_stream))
             launches += 2 + (1 if phase & 1 else 0) + (2 if phase & 2 else 0)
+            if last:
+                self.collective_end.record(self.communication_stream)
             if index > 0:
                 launches += self._result_final(index - 1, gradient, host_payload, self.write_fp32,
                                                self.final_events[index - 1])

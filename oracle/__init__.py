@@ -54,15 +54,16 @@ def build(force: bool = False) -> str:
     raise RuntimeError("could not build the CPU oracle:\n" + "\n".join(errors))
 
 
-def build_reference_kernels() -> str | None:
+def build_reference_kernels(reference_root: str | None = None) -> str | None:
     """Compile the reference's own CUDA kernels (unmodified) into
-    oracle/_ref/libref_grad.so when the reference tree is mounted; otherwise
-    keep whatever prebuilt file is there.  Returns its path or None."""
+    oracle/_ref/libref_grad.so from the reference tree at `reference_root` (or
+    $NNTRAIN_REFERENCE_ROOT); without a tree keep whatever prebuilt file is
+    there.  Returns its path or None."""
     script = os.path.join(_HERE, "build_ref.sh")
     target = os.path.join(_HERE, "_ref", "libref_grad.so")
-    root = os.environ.get("NNTRAIN_REFERENCE_ROOT", "/root/reference")
-    if os.path.isdir(root) and not os.path.exists(target):
-        subprocess.run(["bash", script], check=True)
+    root = reference_root or os.environ.get("NNTRAIN_REFERENCE_ROOT", "")
+    if root and os.path.isdir(root) and not os.path.exists(target):
+        subprocess.run(["bash", script], check=True, env=dict(os.environ, NNTRAIN_REFERENCE_ROOT=root))
     return target if os.path.exists(target) else None
 
 

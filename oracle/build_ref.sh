@@ -9,7 +9,11 @@
 # reference's own build script (build-cuda.ps1: -O3 --use_fast_math -std=c++17)
 # with only the target architecture changed.  No reference source is copied.
 set -euo pipefail
-REF_ROOT="${NNTRAIN_REFERENCE_ROOT:-/root/reference}"
+REF_ROOT="${NNTRAIN_REFERENCE_ROOT:-}"
+if [ -z "$REF_ROOT" ]; then
+  echo "set NNTRAIN_REFERENCE_ROOT to the reference project's root" >&2
+  exit 0
+fi
 SRC="$REF_ROOT/NNtrain.Cuda/native"
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 OUT="$HERE/_ref"

@@ -128,3 +128,73 @@ def test_ranges_beyond_the_fixed_scratch_are_refused(cuda, lib):
     from nntrain_b200.library import last_error
     info = last_error()
     assert info.status == 1 and info.operation == 200
+
+
+def both_entries_on(payloads, scales, first, end, block, scale, outputs=1, offset_bytes=0):
+    """Runs both entry points over [first, end) with `outputs` destinations
+    each; returns per entry (list of payload arrays, list of scale arrays, sum,
+    flag).  offset_bytes shifts every payload pointer off its 16-byte alignment."""
+    n = payloads[0].numel()
+    results = []
+    for entry in (reducers.reduce_shards_bfp8, reducers.reduce_shards_bfp8_no_alloc):
+        holders = [torch.zeros(n + 64, dtype=torch.int8, device="cuda") for _ in range(outputs)]
+        out_p = [h[offset_bytes:offset_bytes + n] for h in holders]
+        out_s = [torch.zeros(scale_count(n, block), dtype=torch.float32, device="cuda") for _ in range(outputs)]
+        sq = torch.zeros(1, dtype=torch.float64, device="cuda")
+        flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+        entry(0, payloads, scales, out_p, out_s, first, end, block, scale, sq, flag)
+        torch.cuda.synchronize()
+        results.append(([host(p) for p in out_p], [host(s) for s in out_s], float(sq.item()), int(flag.item())))
+    return results
+
+
+def check_against_oracle(oracle, results, gradients, first, end, block, scale):
+    regular, static = results
+    expect_payload, expect_scales, _, _ = oracle.allreduce_bfp8(gradients, block, scale)
+    sa, sb = first // block, (end + block - 1) // block
+    expect_sq = oracle.squared_sum_bfp8(expect_payload[first:end], expect_scales[sa:sb], block)
+    for d in range(len(static[0])):
+        assert_bits_equal(static[0][d][first:end], regular[0][d][first:end], f"payload, output {d}")
+        assert_bits_equal(static[1][d][sa:sb], regular[1][d][sa:sb], f"scales, output {d}")
+        assert_bits_equal(static[0][d][first:end], expect_payload[first:end], f"payload vs oracle, output {d}")
+        assert_bits_equal(static[1][d][sa:sb], expect_scales[sa:sb], f"scales vs oracle, output {d}")
+        # nothing outside the range is written
+        assert not static[0][d][:first].any() and not static[0][d][end:].any()
+    assert static[3] == regular[3] == 0
+    assert static[2] == pytest.approx(regular[2], rel=1e-12)
+    assert static[2] == pytest.approx(expect_sq, rel=1e-12)
+
+
+def test_a_shard_in_the_middle_of_the_arena_with_a_ragged_end(cuda, oracle):
+    # what the owner of the last shard passes: a 512-aligned first value and the
+    # arena's ragged end (its last block is a partial one)
+    world, block, n = 3, 32, 7 * 65536 + 300
+    gradients = [oracle.generate_gradient(n, 0xB2000014, r) for r in range(world)]
+    payloads, scales = encoded_replicas(oracle, world, n, block, seed_shift=4)
+    first, end = 512 * 259, n
+    for _ in range(2):        # two calls in a row share the scratch
+        results = both_entries_on(payloads, scales, first, end, block, 1.0 / world)
+        check_against_oracle(oracle, results, gradients, first, end, block, 1.0 / world)
+
+
+def test_payload_pointers_off_their_16_byte_alignment(cuda, oracle):
+    # pointers offset by 4 bytes force the scalar path of the kernel
+    world, block, n = 2, 32, 65536 + 96
+    gradients = [oracle.generate_gradient(n, 0xB2000015, r) for r in range(world)]
+    aligned_p, scales = encoded_replicas(oracle, world, n, block, seed_shift=5)
+    payloads = []
+    for p in aligned_p:
+        holder = torch.zeros(n + 64, dtype=torch.int8, device="cuda")
+        holder[4:4 + n].copy_(p)
+        payloads.append(holder[4:4 + n])
+        assert payloads[-1].data_ptr() % 16 == 4
+    results = both_entries_on(payloads, scales, 0, n, block, 0.5, offset_bytes=4)
+    check_against_oracle(oracle, results, gradients, 0, n, block, 0.5)
+
+
+def test_block_64_with_two_outputs(cuda, oracle):
+    world, block, n = 4, 64, 3 * 65536 + 64 * 5
+    gradients = [oracle.generate_gradient(n, 0xB2000016, r) for r in range(world)]
+    payloads, scales = encoded_replicas(oracle, world, n, block, seed_shift=6)
+    results = both_entries_on(payloads, scales, 1024, n, block, 0.25, outputs=2)
+    check_against_oracle(oracle, results, gradients, 1024, n, block, 0.25)

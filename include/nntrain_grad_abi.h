@@ -145,6 +145,39 @@ int nntrain_bfp8_gradient_broadcast(
     float* destination_float, int length, int* destination_finite_status,
     nntrain_stream_t destination_stream, nntrain_event_t source_ready);
 
+/* ABI minor 36: the three calls above for EVERY tensor of a bucket at once.
+ * The reference publishes, reduces and broadcasts one tensor per call
+ * (tensor_kernels.cu:1114-1146: a memset and five or six launches per tensor;
+ * :3935-4038: about thirteen; NNtrain.Core/Tensors/
+ * CudaBfp8GradientPublicationScope.cs:12-521 walks the leaves the same way).
+ * The tensors of a bucket lie in one contiguous arena at running-sum offsets
+ * (NNtrain.Core/Training/CudaBFloat16GradientAllReduce.cs:1572-1601);
+ * tensor_offsets is a DEVICE array of tensors + 1 strictly ascending element
+ * offsets (first 0, last total_elements); payload has the arena's layout,
+ * scales one entry per tensor; maxima_scratch is tensors words owned by the
+ * caller.  Each call is three stream operations per bucket.  A NaN / Inf
+ * anywhere in the bucket raises *finite_status and publishes nothing (every
+ * scale of the bucket = 1). */
+int nntrain_bfp8_gradient_publish_tensors(
+    int device, float* arena, signed char* payload, float* scales, const long long* tensor_offsets,
+    int tensors, long long total_elements, unsigned* maxima_scratch, int* finite_status,
+    double* squared_sum, nntrain_stream_t stream);
+/* reduced = reduction_scale * (rank-ordered fp32 sum of code * scale) over N
+ * encoded inputs (host tables of device pointers; per-tensor scale arrays),
+ * then published as above into out_payload / out_scales; `reduced` ends as the
+ * decode of the result. */
+int nntrain_bfp8_gradient_reduce_tensors(
+    int device, int inputs, const signed char* const* payloads, const float* const* scales,
+    float* reduced, signed char* out_payload, float* out_scales, const long long* tensor_offsets,
+    int tensors, long long total_elements, float reduction_scale, unsigned* maxima_scratch,
+    int* finite_status, double* squared_sum, nntrain_stream_t stream);
+/* destination = payload * scales[tensor] for a whole bucket; skipped when
+ * *skip_flag (optional) is non-zero (tensor_kernels.cu:4034-4036). */
+int nntrain_bfp8_gradient_decode_tensors(
+    int device, const signed char* payload, const float* scales, float* destination,
+    const long long* tensor_offsets, int tensors, long long total_elements, const int* skip_flag,
+    nntrain_stream_t stream);
+
 /* ---- bucketed BF16 / block-128 BFP8 transport (two devices, one process) --- */
 
 /* NNtrain.Cuda/native/gradient_collectives.cu:213-219 */

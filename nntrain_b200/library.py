@@ -43,7 +43,7 @@ _SCALARS = {
     "long long": ctypes.c_longlong, "unsigned long long": ctypes.c_ulonglong,
     "size_t": ctypes.c_size_t, "uint32_t": ctypes.c_uint32, "uint64_t": ctypes.c_uint64,
     "int32_t": ctypes.c_int32, "nntrain_stream_t": ctypes.c_void_p,
-    "nntrain_event_t": ctypes.c_void_p, "unsigned short": ctypes.c_ushort,
+    "nntrain_event_t": ctypes.c_void_p, "unsigned short": ctypes.c_ushort, "unsigned": ctypes.c_uint,
 }
 
 

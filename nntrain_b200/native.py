@@ -129,6 +129,44 @@ class CudaBfp8GradientNative:
                 _ptr(squared_sum), _stream(stream)))
 
     @staticmethod
+    def publish_tensors(device: int, arena, payload, scales, tensor_offsets, maxima_scratch, finite_status,
+                        squared_sum=None, stream=None) -> None:
+        """Every tensor of a bucket arena in three stream operations:
+        `tensor_offsets` is a device int64 tensor of tensors + 1 ascending
+        element offsets, `scales` / `maxima_scratch` have one entry per tensor."""
+        _require(arena, torch.float32, "arena", device)
+        _require(payload, torch.int8, "payload", device)
+        _require(scales, torch.float32, "scales", device)
+        _require(tensor_offsets, torch.int64, "tensor_offsets", device)
+        _require(maxima_scratch, torch.int32, "maxima_scratch", device)
+        tensors = tensor_offsets.numel() - 1
+        if payload.numel() != arena.numel() or scales.numel() != tensors or maxima_scratch.numel() < tensors:
+            raise ValueError("payload / scales / scratch sizes do not match the arena and the offset table")
+        check("bfp8_gradient_publish_tensors", load().nntrain_bfp8_gradient_publish_tensors(
+            device, _ptr(arena), _ptr(payload), _ptr(scales), _ptr(tensor_offsets), tensors, arena.numel(),
+            _ptr(maxima_scratch), _ptr(finite_status), _ptr(squared_sum), _stream(stream)))
+
+    @staticmethod
+    def reduce_tensors(device: int, payloads, scales, reduced, out_payload, out_scales, tensor_offsets,
+                       maxima_scratch, finite_status, reduction_scale: float = 1.0, squared_sum=None,
+                       stream=None) -> None:
+        import ctypes
+        tensors = tensor_offsets.numel() - 1
+        table_p = (ctypes.c_void_p * len(payloads))(*[_ptr(p) for p in payloads])
+        table_s = (ctypes.c_void_p * len(scales))(*[_ptr(s) for s in scales])
+        check("bfp8_gradient_reduce_tensors", load().nntrain_bfp8_gradient_reduce_tensors(
+            device, len(payloads), table_p, table_s, _ptr(reduced), _ptr(out_payload), _ptr(out_scales),
+            _ptr(tensor_offsets), tensors, reduced.numel(), reduction_scale, _ptr(maxima_scratch),
+            _ptr(finite_status), _ptr(squared_sum), _stream(stream)))
+
+    @staticmethod
+    def decode_tensors(device: int, payload, scales, destination, tensor_offsets, skip_flag=None,
+                       stream=None) -> None:
+        check("bfp8_gradient_decode_tensors", load().nntrain_bfp8_gradient_decode_tensors(
+            device, _ptr(payload), _ptr(scales), _ptr(destination), _ptr(tensor_offsets),
+            tensor_offsets.numel() - 1, destination.numel(), _ptr(skip_flag), _stream(stream)))
+
+    @staticmethod
     def accumulate_squared_sum(device: int, payload, scale, squared_sum, finite_status, stream=None) -> None:
         check("bfp8_gradient_squared_sum", load().nntrain_bfp8_gradient_squared_sum(
             device, _ptr(payload), _ptr(scale), payload.numel(), _ptr(squared_sum), _ptr(finite_status),

@@ -99,6 +99,15 @@ int nntrain_cuda_bfp8_dequantize_f32(int device, const signed char* payload, con
 int nntrain_cuda_bfp8_quantize_f32_roundtrip(int device, float* source, signed char* payload,
                                              float* scales, int length, int quantization_block_size,
                                              void* stream);
+/* The codec with a bf16 tensor as the source: the fp32 rules on the widened
+ * value.  cuda_runtime_bridge.cu:868-935,2024-2118 */
+int nntrain_cuda_bfp8_quantize_bf16(int device, const unsigned short* source, signed char* payload,
+                                    float* scales, int length, int quantization_block_size,
+                                    void* stream);
+/* destination = bf16_rn(code * scale).  cuda_runtime_bridge.cu:769-806,1964-2022 */
+int nntrain_cuda_bfp8_dequantize_bf16(int device, const signed char* payload, const float* scales,
+                                      unsigned short* destination, int length,
+                                      int quantization_block_size, void* stream);
 /* ABI minor 36.  64-bit length; block_size 0 = tensor-wide.  Optional
  * outputs, each enabled by a non-null pointer: roundtrip (decode, may alias
  * source), squared_sum (+= sum of squares of the decoded values, binary64),
@@ -357,6 +366,15 @@ int nntrain_gradient_allreduce_bfp8(
     int block_size, float reduction_scale, double* squared_sum, int* finite_status, int mode,
     int phase, signed char* staging_payload, float* staging_scales, nntrain_event_t previous_final,
     nntrain_stream_t stream);
+/* Parameter publication after an optimizer step that is sharded over the
+ * ranks (the reference re-publishes every BFP8 data replica after a step with
+ * every device updating everything, NNtrain.Core/Tensors/
+ * Tensor.Device.Bfp8.cs:593-649): this rank encodes its shard of `source` (its
+ * fp32 master arena) into EVERY rank's encoded arena; afterwards all ranks
+ * hold encode(assembled parameters), bit-identical.  Collective. */
+int nntrain_gradient_publish_shards_bfp8(
+    void* group, const float* source, signed char* const* payload_by_rank, float* const* scales_by_rank,
+    long long length, int block_size, int* finite_status, nntrain_stream_t stream);
 /* Makes `stream` wait for `event` (cudaStreamWaitEvent on opaque handles; the
  * reference does this inside its exchange entry points,
  * NNtrain.Cuda/native/gradient_collectives.cu:284-291). */
@@ -393,6 +411,13 @@ int nntrain_gradient_local_allreduce_bfp8(
 int nntrain_gradient_local_allreduce_bf16(
     void* group, unsigned short* const* values_by_rank, long long length, float reduction_scale,
     double* const* squared_sum_by_rank, int phase, const nntrain_stream_t* streams);
+
+/* The in-process form of nntrain_gradient_publish_shards_bfp8:
+ * source_by_rank[r] is rank r's fp32 master arena. */
+int nntrain_gradient_local_publish_shards_bfp8(
+    void* group, const float* const* source_by_rank, signed char* const* payload_by_rank,
+    float* const* scales_by_rank, long long length, int block_size, int* const* finite_status_by_rank,
+    const nntrain_stream_t* streams);
 
 #ifdef __cplusplus
 }

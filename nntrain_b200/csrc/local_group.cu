@@ -291,3 +291,39 @@ NNTRAIN_EXPORT int nntrain_gradient_local_allreduce_bf16(
         });
     return complete(kOpGradientLocalAllReduce, g->device[0], status);
 }
+
+// Publication of parameters whose optimizer step is sharded over the ranks
+// (the reference re-publishes every BFP8 data replica after a step,
+// NNtrain.Core/Tensors/Tensor.Device.Bfp8.cs:593-649, with every device
+// updating everything; here rank r updates and encodes shard r only): rank r
+// encodes [shard r) of source_by_rank[r] (its fp32 master arena) and stores
+// payload + scales into EVERY rank's encoded arena.  On completion, in stream
+// order on streams[r], every rank holds encode(assembled parameters),
+// bit-identical everywhere.  *finite_status_by_rank[r] (optional) is raised on
+// every rank when any shard held a NaN / Inf.
+NNTRAIN_EXPORT int nntrain_gradient_local_publish_shards_bfp8(
+    void* group, const float* const* source_by_rank, signed char* const* payload_by_rank,
+    float* const* scales_by_rank, long long length, int block_size, int* const* finite_status_by_rank,
+    const cudaStream_t* streams) {
+    LocalGroup* g = static_cast<LocalGroup*>(group);
+    if (!g || g->kind != kKindLocalGroup || !source_by_rank || !payload_by_rank || !scales_by_rank || !streams ||
+        length <= 0 || (block_size != 32 && block_size != 64 && block_size != 128))
+        return complete(kOpGradientLocalAllReduce, -1, static_cast<int>(cudaErrorInvalidValue));
+    EncodedShards shards{};
+    shards.inputs = 0;
+    shards.outputs = g->ranks;
+    for (int k = 0; k < g->ranks; ++k) {
+        if (!source_by_rank[k] || !payload_by_rank[k] || !scales_by_rank[k])
+            return complete(kOpGradientLocalAllReduce, g->device[k], static_cast<int>(cudaErrorInvalidValue));
+        shards.out_payload[k] = payload_by_rank[k];
+        shards.out_scales[k] = scales_by_rank[k];
+    }
+    DeviceScope scope;
+    const CollectiveShape shape{g->shape.ctas, 0, 0};
+    const int status = run_step(g, length, 3, nullptr, finite_status_by_rank, streams,
+        [&](int rank, long long first, long long end, double*, int* flag, cudaStream_t stream) {
+            return launch_bfp8_encode_to_all(source_by_rank[rank], shards, first, end, block_size, flag, stream,
+                                             &shape);
+        });
+    return complete(kOpGradientLocalAllReduce, g->device[0], status);
+}

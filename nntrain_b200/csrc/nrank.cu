@@ -691,6 +691,56 @@ static int gradient_allreduce_bf16_impl(
     return static_cast<int>(cudaPeekAtLastError());
 }
 
+// Publication of parameters whose optimizer step is sharded over the ranks:
+// this rank encodes its shard of `source` (its fp32 master arena) and stores
+// payload + scales into every rank's encoded arena (peer stores); a leading
+// barrier makes sure nobody still reads the previous publication, the closing
+// collective fences the stores and spreads the finite flag.  Collective.
+static int gradient_publish_shards_bfp8_impl(void* group, const float* source, signed char* const* payload_by_rank,
+                                             float* const* scales_by_rank, long long length, int block_size,
+                                             int* finite_status, cudaStream_t stream) {
+    Group* g = static_cast<Group*>(group);
+    if (!g || !source || !payload_by_rank || !scales_by_rank || length <= 0 ||
+        (block_size != 32 && block_size != 64 && block_size != 128))
+        return static_cast<int>(cudaErrorInvalidValue);
+    int status = select_device(g->device);
+    if (status != cudaSuccess) return status;
+    const int world = g->world, rank = g->rank;
+    long long first = 0, end = 0;
+    shard_range(length, world, rank, &first, &end);
+    clear_partials_kernel<<<1, 1, 0, stream>>>(g->scratch, finite_status);
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (world > 1 && (status = barrier(g, stream)) != 0) return status;
+    EncodedShards shards{};
+    shards.outputs = world;
+    for (int k = 0; k < world; ++k) {
+        if (!payload_by_rank[k] || !scales_by_rank[k]) return static_cast<int>(cudaErrorInvalidValue);
+        shards.out_payload[k] = payload_by_rank[k];
+        shards.out_scales[k] = scales_by_rank[k];
+    }
+    if (end > first) {
+        const CollectiveShape shape{g->shape.ctas, 0, 0};
+        e = launch_bfp8_encode_to_all(source, shards, first, end, block_size, reinterpret_cast<int*>(g->scratch + 3),
+                                      stream, &shape);
+        if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    fold_flags_kernel<<<1, 1, 0, stream>>>(g->scratch, finite_status);
+    if ((e = cudaPeekAtLastError()) != cudaSuccess) return static_cast<int>(e);
+    if (world > 1 && (status = sum_partials(g, stream)) != 0) return status;
+    publish_totals_kernel<<<1, 1, 0, stream>>>(g->scratch, nullptr, finite_status);
+    return static_cast<int>(cudaPeekAtLastError());
+}
+
+NNTRAIN_EXPORT int nntrain_gradient_publish_shards_bfp8(void* group, const float* source,
+                                                        signed char* const* payload_by_rank,
+                                                        float* const* scales_by_rank, long long length,
+                                                        int block_size, int* finite_status, cudaStream_t stream) {
+    return complete(kOpGradientAllReduce, group ? static_cast<Group*>(group)->device : -1,
+                    gradient_publish_shards_bfp8_impl(group, source, payload_by_rank, scales_by_rank, length,
+                                                      block_size, finite_status, stream));
+}
+
 // Sums `count` doubles over the ranks in place (stream-ordered); with
 // count == 0 it is a pure barrier.  For host-side quantities that ride along
 // with a step (global norm pieces, flags).

@@ -251,6 +251,94 @@ bfp8_reduce_reencode_kernel(EncodedShards shards, long long first_value, long lo
     if (kSquares) cta_accumulate(squares, squared_sum);
 }
 
+// ---- encode + all-gather: fp32 shard -> encoded shard in every arena -------------
+// The publication of updated parameters after an optimizer step that is
+// sharded over the ranks (every rank updates the fp32 master of its own shard
+// only): rank r encodes shard r of its fp32 arena and stores payload + scales
+// into EVERY rank's encoded arena with 128-bit (peer) stores -- the all-gather
+// half of the fused all-reduce kernel with the encode in front of it.  Same
+// tiling: a lane owns 16 consecutive values (four 128-bit fp32 loads, issued
+// for the next tile before the current one is encoded), a warp 512.
+struct Fp32Tile {
+    float4 v[4];
+};
+
+__device__ __forceinline__ void load_fp32_tile(const float* __restrict__ source, long long base, int lane,
+                                               Fp32Tile& tile) {
+    const float* p = source + base + lane * 16;
+    #pragma unroll
+    for (int q = 0; q < 4; ++q) tile.v[q] = load_f4_stream(p + q * 4);
+}
+
+template <int kBlock>
+__global__ void __launch_bounds__(kThreads)
+bfp8_encode_to_all_kernel(const float* __restrict__ source, EncodedShards shards, long long first_value,
+                          long long end_value, int* finite_status, bool vector_ok) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = static_cast<long long>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
+    const long long warps = static_cast<long long>(gridDim.x) * kWarpsPerCta;
+    const long long tiles = (end_value - first_value + 511) / 512;
+    double unused = 0.0;
+    int non_finite = 0;
+    auto is_fast = [&](long long tile) {
+        return vector_ok && tile < tiles && first_value + tile * 512 + 512 <= end_value;
+    };
+    Fp32Tile current, next;
+    long long tile = warp;
+    bool current_fast = is_fast(tile);
+    if (current_fast) load_fp32_tile(source, first_value + tile * 512, lane, current);
+    while (tile < tiles) {
+        const long long following = tile + warps;
+        const bool next_fast = is_fast(following);
+        if (next_fast) load_fp32_tile(source, first_value + following * 512, lane, next);
+        const long long base = first_value + tile * 512;
+        if (current_fast) {
+            float acc[16];
+            #pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                acc[q * 4 + 0] = current.v[q].x; acc[q * 4 + 1] = current.v[q].y;
+                acc[q * 4 + 2] = current.v[q].z; acc[q * 4 + 3] = current.v[q].w;
+            }
+            // x * 1 is x: the shared tail re-encodes "reduction_scale * sum"
+            reencode_and_store<kBlock, false>(shards, base, lane, acc, 1.0f, unused, non_finite);
+        } else {
+            // ragged end / unaligned pointers: one block at a time, scalar
+            const long long tile_end = base + 512 < end_value ? base + 512 : end_value;
+            for (long long start = base; start < tile_end; start += kBlock) {
+                const long long stop = start + kBlock < end_value ? start + kBlock : end_value;
+                constexpr int kPerLane = kBlock / 32;
+                float value[kPerLane];
+                float m = 0.0f;
+                #pragma unroll
+                for (int e = 0; e < kPerLane; ++e) {
+                    const long long i = start + lane + e * 32;
+                    value[e] = i < stop ? source[i] : 0.0f;
+                    non_finite |= is_non_finite(value[e]);
+                    m = fmaxf(m, fabsf(value[e]));
+                }
+                m = group_max<32>(m);
+                const float scale = scale_from_maximum(m);
+                #pragma unroll
+                for (int e = 0; e < kPerLane; ++e) {
+                    const long long i = start + lane + e * 32;
+                    if (i < stop) {
+                        const signed char code = code_byte(biased_code_of(value[e], scale));
+                        for (int d = 0; d < shards.outputs; ++d) shards.out_payload[d][i] = code;
+                    }
+                }
+                if (lane == 0)
+                    for (int d = 0; d < shards.outputs; ++d) shards.out_scales[d][start / kBlock] = scale;
+            }
+        }
+        current = next;
+        current_fast = next_fast;
+        tile = following;
+    }
+    if (finite_status != nullptr) {
+        if (__any_sync(0xffffffffu, non_finite) && lane == 0) atomicExch(finite_status, 1);
+    }
+}
+
 // ---- asynchronous-copy variant ------------------------------------------------
 // Same arithmetic; the inputs travel global -> shared memory with cp.async
 // (16-byte payload pieces, 4-byte scales) through a ring of kStages tiles per
@@ -617,6 +705,12 @@ cudaError_t launch_bfp8_reduce_reencode(const EncodedShards& shards, long long f
                                         long long end_value, int block, float reduction_scale,
                                         double* squared_sum, int* finite_status, cudaStream_t stream,
                                         const CollectiveShape* shape = nullptr);
+
+// fp32 [first_value, end_value) of `source` -> payload + scales in every output
+// of `shards` (inputs unused).  first_value must be a multiple of `block`.
+cudaError_t launch_bfp8_encode_to_all(const float* source, const EncodedShards& shards, long long first_value,
+                                      long long end_value, int block, int* finite_status, cudaStream_t stream,
+                                      const CollectiveShape* shape = nullptr);
 
 cudaError_t launch_bfp8_sum_to_f32(const EncodedInputs& in, float* reduced, long long length,
                                    long long block, float reduction_scale, double* squared_sum,

@@ -158,6 +158,29 @@ cudaError_t launch_bfp8_reduce_reencode(const EncodedShards& shards, long long f
     }
 }
 
+cudaError_t launch_bfp8_encode_to_all(const float* source, const EncodedShards& shards, long long first_value,
+                                      long long end_value, int block, int* finite_status, cudaStream_t stream,
+                                      const CollectiveShape* shape_or_null) {
+    const CollectiveShape shape = shape_or_null ? *shape_or_null : default_collective_shape();
+    if (!source || shards.outputs < 1 || shards.outputs > kMaxRanks) return cudaErrorInvalidValue;
+    if (first_value < 0 || end_value <= first_value) return cudaErrorInvalidValue;
+    if ((block != 32 && block != 64 && block != 128) || first_value % block != 0) return cudaErrorInvalidValue;
+    bool vector_ok = first_value % 16 == 0 && aligned_to(source, 16);
+    for (int d = 0; d < shards.outputs; ++d) {
+        if (!shards.out_payload[d] || !shards.out_scales[d]) return cudaErrorInvalidValue;
+        vector_ok = vector_ok && aligned_to(shards.out_payload[d], 16);
+    }
+    const long long tiles = (end_value - first_value + 511) / 512;
+    const int grid = capped_grid((tiles + kWarpsPerCta - 1) / kWarpsPerCta, shape.ctas, kCtasPerSmDefault);
+    if (block == 32)
+        bfp8_encode_to_all_kernel<32><<<grid, kThreads, 0, stream>>>(source, shards, first_value, end_value, finite_status, vector_ok);
+    else if (block == 64)
+        bfp8_encode_to_all_kernel<64><<<grid, kThreads, 0, stream>>>(source, shards, first_value, end_value, finite_status, vector_ok);
+    else
+        bfp8_encode_to_all_kernel<128><<<grid, kThreads, 0, stream>>>(source, shards, first_value, end_value, finite_status, vector_ok);
+    return cudaPeekAtLastError();
+}
+
 cudaError_t launch_bfp8_sum_to_f32(const EncodedInputs& in, float* reduced, long long length,
                                    long long block, float reduction_scale, double* squared_sum,
                                    int* finite_status, unsigned* maximum_bits, cudaStream_t stream) {

@@ -75,6 +75,28 @@ class CudaBfp8Native:
             device, _ptr(payload), _ptr(scales), _ptr(destination), n, block, _stream(stream)))
 
     @staticmethod
+    def quantize_bfloat16(device: int, source_bits, payload, scales, block_size: int, stream=None) -> None:
+        """`source_bits`: bf16 bit patterns (int16 tensor)."""
+        _require(source_bits, torch.int16, "source", device)
+        _require(payload, torch.int8, "payload", device)
+        n = source_bits.numel()
+        if payload.numel() != n or scales.numel() != scale_count(n, block_size):
+            raise ValueError("BFP8 payload / scale lengths do not match the descriptor")
+        check("cuda_bfp8_quantize_bf16", load().nntrain_cuda_bfp8_quantize_bf16(
+            device, _ptr(source_bits), _ptr(payload), _ptr(scales), n, n if block_size <= 0 else block_size,
+            _stream(stream)))
+
+    @staticmethod
+    def dequantize_bfloat16(device: int, payload, scales, destination_bits, block_size: int, stream=None) -> None:
+        _require(destination_bits, torch.int16, "destination", device)
+        n = payload.numel()
+        if destination_bits.numel() != n or scales.numel() != scale_count(n, block_size):
+            raise ValueError("BFP8 payload / scale lengths do not match the descriptor")
+        check("cuda_bfp8_dequantize_bf16", load().nntrain_cuda_bfp8_dequantize_bf16(
+            device, _ptr(payload), _ptr(scales), _ptr(destination_bits), n, n if block_size <= 0 else block_size,
+            _stream(stream)))
+
+    @staticmethod
     def quantize_float32_roundtrip(device: int, state, payload, scales, block_size: int, stream=None) -> None:
         _require(state, torch.float32, "state", device)
         _require(payload, torch.int8, "payload", device)

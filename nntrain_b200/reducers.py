@@ -113,6 +113,14 @@ class GradientGroup:
         """Gives the communicator up without waiting (a peer was declared lost)."""
         check("gradient_group_abort", load().nntrain_gradient_group_abort(self.handle))
 
+    def publish_shards_bfp8(self, source: torch.Tensor, payload_pointers, scales_pointers, length: int,
+                            block_size: int, finite_status=None, stream=None) -> None:
+        """This rank encodes its shard of `source` (fp32) into every rank's
+        encoded arena; collective."""
+        check("gradient_publish_shards_bfp8", load().nntrain_gradient_publish_shards_bfp8(
+            self.handle, source.data_ptr(), _pointer_table(payload_pointers), _pointer_table(scales_pointers),
+            length, block_size, 0 if finite_status is None else finite_status.data_ptr(), _stream(stream)))
+
     def sum(self, values: torch.Tensor, stream=None) -> None:
         check("gradient_group_sum", load().nntrain_gradient_group_sum(
             self.handle, values.data_ptr(), values.numel(), _stream(stream)))
@@ -604,6 +612,15 @@ class LocalGradientGroup:
             self.handle, _pointer_table(value_pointers), length, reduction_scale,
             _pointer_table(squared_sum_pointers) if squared_sum_pointers else None, phase,
             _pointer_table(streams)))
+
+    def publish_shards_bfp8(self, source_pointers, payload_pointers, scales_pointers, length: int,
+                            block_size: int, finite_status_pointers, streams) -> None:
+        """Rank r encodes shard r of its fp32 arena into every rank's encoded
+        arena (parameter publication after a sharded optimizer step)."""
+        check("gradient_local_publish_shards_bfp8", load().nntrain_gradient_local_publish_shards_bfp8(
+            self.handle, _pointer_table(source_pointers), _pointer_table(payload_pointers),
+            _pointer_table(scales_pointers), length, block_size,
+            _pointer_table(finite_status_pointers) if finite_status_pointers else None, _pointer_table(streams)))
 
     def close(self) -> None:
         if self.handle:

@@ -225,3 +225,41 @@ def test_scale_is_the_ieee_quotient_for_every_significand(cuda, exponent_bits):
     assert_bits_equal(host(scales), expect, "scales")
     codes = host(payload[7::32])
     assert (codes == -127).all()
+
+
+@pytest.mark.parametrize("n", (1, 33, 515, 4099, 300137))
+@pytest.mark.parametrize("block", (0, 32, 64, 96, 128))
+def test_bf16_source_codec_matches_the_fp32_rules_on_the_widened_value(cuda, oracle, n, block):
+    # NNtrain.Cuda/native/cuda_runtime_bridge.cu:868-935 (encode), 769-806 (decode to bf16)
+    bits = oracle.bf16_encode(vectors.codec_vector(n) if n <= 515 else vectors.config0_gradient(oracle, 0, n), 1)
+    widened = oracle.bf16_decode(bits)
+    expect_payload, expect_scales = oracle.encode(widened, block, strict=False)
+    source = torch.from_numpy(bits.view(np.int16)).cuda()
+    payload = torch.zeros(n, dtype=torch.int8, device="cuda")
+    scales = torch.zeros(scale_count(n, block), dtype=torch.float32, device="cuda")
+    CudaBfp8Native.quantize_bfloat16(0, source, payload, scales, block)
+    back = torch.zeros(n, dtype=torch.int16, device="cuda")
+    CudaBfp8Native.dequantize_bfloat16(0, payload, scales, back, block)
+    torch.cuda.synchronize()
+    assert_bits_equal(host(payload), expect_payload, "payload")
+    assert_bits_equal(host(scales), expect_scales, "scales")
+    expect_back = oracle.bf16_encode(oracle.decode(expect_payload, expect_scales, block, strict=False), 1)
+    assert_bits_equal(host(back).view(np.uint16), expect_back, "bf16 decode")
+
+
+def test_bf16_source_codec_on_misaligned_buffers(cuda, oracle):
+    n, block = 70001, 32
+    bits = oracle.bf16_encode(vectors.config0_gradient(oracle, 1, n), 1)
+    source = misaligned(n, torch.int16, 1)
+    source.copy_(torch.from_numpy(bits.view(np.int16)))
+    payload = misaligned(n, torch.int8, 3)
+    scales = torch.zeros(scale_count(n, block), dtype=torch.float32, device="cuda")
+    CudaBfp8Native.quantize_bfloat16(0, source, payload, scales, block)
+    back = misaligned(n, torch.int16, 1)
+    CudaBfp8Native.dequantize_bfloat16(0, payload, scales, back, block)
+    torch.cuda.synchronize()
+    expect_payload, expect_scales = oracle.encode(oracle.bf16_decode(bits), block, strict=False)
+    assert_bits_equal(host(payload), expect_payload, "payload")
+    assert_bits_equal(host(scales), expect_scales, "scales")
+    assert_bits_equal(host(back).view(np.uint16),
+                      oracle.bf16_encode(oracle.decode(expect_payload, expect_scales, block, strict=False), 1), "bf16")

@@ -165,3 +165,34 @@ def test_two_groups_keep_their_own_launch_shape(cuda, oracle):
         step.close()
     first.close()
     second.close()
+
+
+@pytest.mark.parametrize("world", (2, 3, 8))
+@pytest.mark.parametrize("n,block", ((515, 32), (70001, 32), ((1 << 20) + 4096 + 13, 32), (1 << 18, 128)))
+def test_parameter_publication_after_a_sharded_step(cuda, oracle, world, n, block):
+    """Rank r owns shard r of the fp32 master parameters; after the fused
+    encode + all-gather every rank holds the encoding of the assembled vector."""
+    masters = [vectors.config0_gradient(oracle, r, n, seed=0xB2000031) for r in range(world)]
+    assembled = np.empty(n, np.float32)
+    for rank in range(world):
+        first, end = reducers.shard_range(n, world, rank)
+        assembled[first:end] = masters[rank][first:end]
+    expect_payload, expect_scales = oracle.encode(assembled, block, strict=False)
+    for devices in device_lists(world):
+        group = reducers.LocalGradientGroup(devices)
+        sources = [to(d, m) for d, m in zip(devices, masters)]
+        payloads = [torch.zeros(n, dtype=torch.int8, device=f"cuda:{d}") for d in devices]
+        scales = [torch.zeros((n + block - 1) // block, dtype=torch.float32, device=f"cuda:{d}") for d in devices]
+        flags = [torch.zeros(1, dtype=torch.int32, device=f"cuda:{d}") for d in devices]
+        streams = [torch.cuda.Stream(d) for d in devices]
+        for _ in range(2):
+            group.publish_shards_bfp8([s.data_ptr() for s in sources], [p.data_ptr() for p in payloads],
+                                      [s.data_ptr() for s in scales], n, block, [f.data_ptr() for f in flags],
+                                      [s.cuda_stream for s in streams])
+        for d in set(devices):
+            torch.cuda.synchronize(d)
+        for rank in range(world):
+            assert_bits_equal(host(payloads[rank]), expect_payload, f"payload on rank {rank}")
+            assert_bits_equal(host(scales[rank]), expect_scales, f"scales on rank {rank}")
+            assert int(flags[rank].item()) == 0
+        group.close()

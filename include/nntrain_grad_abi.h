@@ -282,6 +282,19 @@ int nntrain_gradient_clip_coefficient(int device, const double* squared_sum, flo
 int nntrain_gradient_clip_apply(int device, int kind, void* values, long long count, float multiplier,
                                 const float* coefficient, nntrain_stream_t stream);
 
+/* ABI minor 36.  AdamW that reads the reduced BFP8 gradient directly: the
+ * arithmetic of the reference's adamw_kernel (NNtrain.Cuda/native/
+ * tensor_kernels.cu:1148-1174, export :3233-3241) with g = code * scale formed
+ * in registers, so the step needs no fp32 decode pass (the reference's
+ * BFP8-native optimizers do the same, tensor_kernels.cu:3282-3365).  Every
+ * operation is a separate IEEE binary32 operation.  block_size 0 = one scale
+ * for all; compute_bf16 (optional) receives the bf16 working copy. */
+int nntrain_optimizer_adamw_bfp8_gradient(
+    int device, float* data, const signed char* gradient_payload, const float* gradient_scales,
+    int block_size, float* first_moment, float* second_moment, unsigned short* compute_bf16,
+    long long length, float beta1, float beta2, float learning_rate, float weight_decay,
+    float update_scale, float scaled_epsilon, int apply_weight_decay, nntrain_stream_t stream);
+
 /* ---- N-rank all-reduce, one process per GPU (ABI minor 36) -------------------
  * The reference's compressed reducers accept exactly two devices of one
  * process (NNtrain.Core/Training/CudaBfp8GradientAllReduce.cs:44-49,

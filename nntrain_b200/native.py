@@ -346,3 +346,23 @@ class GradientNorm:
     def clip_apply(device: int, kind: int, values, multiplier: float = 1.0, coefficient=None, stream=None) -> None:
         check("gradient_clip_apply", load().nntrain_gradient_clip_apply(
             device, kind, _ptr(values), values.numel(), multiplier, _ptr(coefficient), _stream(stream)))
+
+
+class Bfp8GradientOptimizers:
+    """Optimizer heads that read the reduced BFP8 gradient without a decode pass."""
+
+    @staticmethod
+    def adamw(device: int, data, gradient_payload, gradient_scales, block_size: int, first_moment, second_moment,
+              beta1: float, beta2: float, learning_rate: float, weight_decay: float, update_scale: float,
+              scaled_epsilon: float, apply_weight_decay: bool = True, compute_bf16=None, stream=None) -> None:
+        for name, t in (("data", data), ("first_moment", first_moment), ("second_moment", second_moment)):
+            _require(t, torch.float32, name, device)
+        _require(gradient_payload, torch.int8, "gradient_payload", device)
+        n = data.numel()
+        if (gradient_payload.numel() != n or first_moment.numel() != n or second_moment.numel() != n
+                or gradient_scales.numel() != scale_count(n, block_size)):
+            raise ValueError("parameter, moment and gradient sizes do not match")
+        check("optimizer_adamw_bfp8_gradient", load().nntrain_optimizer_adamw_bfp8_gradient(
+            device, _ptr(data), _ptr(gradient_payload), _ptr(gradient_scales), block_size, _ptr(first_moment),
+            _ptr(second_moment), _ptr(compute_bf16), n, beta1, beta2, learning_rate, weight_decay, update_scale,
+            scaled_epsilon, int(apply_weight_decay), _stream(stream)))

@@ -291,3 +291,21 @@ def generate_gradient(length: int, seed: int, replica: int = 0, offset: int = 0,
     lib().oracle_generate_gradient(_p(out), length, offset, total, seed, replica, slice_elements,
                                    sigma_lo, sigma_hi, outlier_fraction, zero_fraction, subnormals)
     return out
+
+
+def adamw_step(data, gradient, first_moment, second_moment, beta1, beta2, learning_rate, weight_decay,
+               update_scale, scaled_epsilon, apply_weight_decay=True):
+    """One AdamW step in binary32, operation by operation as the reference's
+    adamw_kernel writes it (NNtrain.Cuda/native/tensor_kernels.cu:1148-1174),
+    every operation rounded separately.  Returns (data, first, second)."""
+    f = np.float32
+    g = _c(gradient, np.float32).ravel()
+    p, m, v = (np.array(a, np.float32, copy=True).ravel() for a in (data, first_moment, second_moment))
+    b1, b2 = f(beta1), f(beta2)
+    first = (b1 * m).astype(f) + ((f(1) - b1) * g).astype(f)
+    second = (b2 * v).astype(f) + (((f(1) - b2) * g).astype(f) * g).astype(f)
+    if apply_weight_decay:
+        p = (p * (f(1) - f(learning_rate) * f(weight_decay))).astype(f)
+    denominator = (np.sqrt(second).astype(f) + f(scaled_epsilon)).astype(f)
+    p = (p - ((f(update_scale) * first).astype(f) / denominator).astype(f)).astype(f)
+    return p, first.astype(f), second.astype(f)

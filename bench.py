@@ -80,7 +80,7 @@ def parse_args():
     p.add_argument("--codec-iterations", type=int, default=-1, help="-1 = library default")
     p.add_argument("--collective-ctas", type=int, default=-1, help="-1 = library default for the run")
     p.add_argument("--collective-async", type=int, default=-1,
-                   help="1 = cp.async ring all-reduce kernel, 0 = register prefetch, -1 = default for the run")
+                   help="all-reduce kernel: 0 = register prefetch, 1 = cp.async rings, 2 = bulk copies, -1 = default")
     p.add_argument("--collective-exclusive", type=int, default=-1,
                    help="1 = the all-reduce kernel's CTAs take whole SMs, 0 = shared, -1 = default for the run")
     p.add_argument("--codec-ctas", type=int, default=0, help="cap on persistent codec grids (0 = none)")
@@ -876,7 +876,7 @@ def run_bf16_bench(args, world, rank, local_rank, barrier):
     step = reducers.Bf16ArenaAllReduce(group, E, reducers.PEER, reduction_scale=1.0 / world,
                                        chunk_elements=args.chunk_elements or None)
     if world > 1 and (args.collective_ctas >= 0 or args.collective_async >= 0):
-        group.configure(max(0, args.collective_ctas), args.collective_async != 0, False)
+        group.configure(max(0, args.collective_ctas), 1 if args.collective_async != 0 else 0, False)
     generator = torch.Generator(device=device)
     generator.manual_seed(0xB2000002 * 1000003 + rank)
     pristine = (torch.randn(E, device=device, generator=generator) * 1e-3).to(torch.bfloat16).view(torch.int16)
@@ -1033,7 +1033,7 @@ def run_interference(args, world, rank, local_rank, barrier):
     from nntrain_b200.library import check, load
     check("configure", load().nntrain_gradient_configure(2, step.collective_ctas))
     check("configure", load().nntrain_gradient_configure_collective(
-        2 if step.collective_exclusive else int(bool(step.collective_async))))
+        3 if step.collective_async == 2 else (2 if step.collective_exclusive else int(bool(step.collective_async)))))
     first, end = reducers.shard_range(E, world, rank)
     payloads = step.payload_buffer.pointers
     scales = step.scales_buffer.pointers

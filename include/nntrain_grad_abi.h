@@ -74,7 +74,8 @@ int nntrain_gradient_configure(int codec_iterations_per_cta, int collective_ctas
 /* ABI minor 36; no counterpart in the reference.  How the owner / all-reduce
  * kernels fetch their inputs when no group says otherwise: 1 (default) =
  * cp.async rings in shared memory, 0 = register prefetch, 2 = cp.async rings
- * in CTAs that take a whole SM each.  Same results either way. */
+ * in CTAs that take a whole SM each, 3 = bulk asynchronous copies of whole
+ * tiles (CTAs own their SM).  Same results either way. */
 int nntrain_gradient_configure_collective(int asynchronous_copies);
 /* ABI minor 36; no counterpart in the reference.  Most CTAs a persistent
  * encode / decode grid may use (only with codec_iterations_per_cta == 0);
@@ -319,9 +320,10 @@ int nntrain_gradient_group_create(const void* id128, int world, int rank, int de
 int nntrain_gradient_group_destroy(void* group);
 /* Launch shape of ONE group's all-reduce kernels (either kind of group), so
  * that two reducers in a process do not retune each other.  collective_ctas:
- * 0 = fill the machine, n > 0 = at most n CTAs.  asynchronous_copies: 1 =
- * cp.async rings, 0 = register prefetch.  exclusive_sms (needs
- * asynchronous_copies): every CTA asks for a whole SM's shared memory, so
+ * 0 = fill the machine, n > 0 = at most n CTAs.  asynchronous_copies: 0 =
+ * register prefetch, 1 = cp.async rings, 2 = bulk asynchronous copies of whole
+ * tiles (always exclusive).  exclusive_sms (needs asynchronous_copies): every
+ * CTA asks for a whole SM's shared memory, so
  * collective_ctas SMs belong to the all-reduce while it runs and the encode /
  * decode kernels of neighbouring chunks never share an SM with it. */
 int nntrain_gradient_group_configure(void* group, int collective_ctas, int asynchronous_copies,

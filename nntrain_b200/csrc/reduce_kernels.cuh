@@ -81,14 +81,13 @@ __device__ __forceinline__ void load_shard_tile(const EncodedShards& shards, lon
     }
 }
 
-// Re-encodes acc[16] (already summed and scaled) and stores payload + scale to
-// every destination.
+// Re-encodes acc[16] (the rank-ordered sums): x reduction_scale, block scale,
+// 16 codes packed into one 128-bit word; optional sum of squares of the
+// decoded result.
 template <int kBlock, bool kSquares>
-__device__ __forceinline__ void reencode_and_store(const EncodedShards& shards, long long base, int lane,
-                                                   float (&acc)[16], float reduction_scale,
-                                                   double& squares, int& non_finite) {
+__device__ __forceinline__ void reencode16(float (&acc)[16], float reduction_scale, double& squares,
+                                           int& non_finite, uint4& packed, float& scale) {
     constexpr int kLanesPerBlock = kBlock / 16;
-    const long long at = base + lane * 16;
     float m = 0.0f;
     #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -99,14 +98,13 @@ __device__ __forceinline__ void reencode_and_store(const EncodedShards& shards, 
     m = group_max<kLanesPerBlock>(m);
     // a NaN sum is dropped by fmaxf and an Inf one gives scale = Inf; both are
     // flagged above and take the exact per-value path inside biased_codes_of
-    const float scale = scale_from_maximum_fast(m);
+    scale = scale_from_maximum_fast(m);
     const BlockScale divisor = block_scale(scale);
     float t[16];
     #pragma unroll
     for (int i = 0; i < 16; i += 4)
         biased_codes_of(make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]), divisor,
                         t[i], t[i + 1], t[i + 2], t[i + 3]);
-    uint4 packed;
     packed.x = pack_codes(t[0], t[1], t[2], t[3]);
     packed.y = pack_codes(t[4], t[5], t[6], t[7]);
     packed.z = pack_codes(t[8], t[9], t[10], t[11]);
@@ -118,6 +116,18 @@ __device__ __forceinline__ void reencode_and_store(const EncodedShards& shards, 
             squares += d * d;
         }
     }
+}
+
+// Re-encodes acc[16] and stores payload + scale to every destination.
+template <int kBlock, bool kSquares>
+__device__ __forceinline__ void reencode_and_store(const EncodedShards& shards, long long base, int lane,
+                                                   float (&acc)[16], float reduction_scale,
+                                                   double& squares, int& non_finite) {
+    constexpr int kLanesPerBlock = kBlock / 16;
+    const long long at = base + lane * 16;
+    uint4 packed;
+    float scale;
+    reencode16<kBlock, kSquares>(acc, reduction_scale, squares, non_finite, packed, scale);
     // Gather the tile's scales (one per kLanesPerBlock lanes) into the low
     // lanes so each destination gets one contiguous store.
     constexpr int kScalesPerTile = 512 / kBlock;
@@ -678,10 +688,11 @@ bf16_reduce_kernel(Bf16Inputs io, float* reduced, long long first_value, long lo
 }
 
 // How an all-reduce kernel is launched.  ctas: 0 = fill the machine, n > 0 =
-// at most n CTAs.  asynchronous: 1 = cp.async rings in shared memory, 0 =
-// register prefetch.  exclusive: 1 (with asynchronous) = big CTAs that take a
-// whole SM each (see kExclusiveSharedBytes), so `ctas` is then the number of
-// SMs the collective owns while it runs.
+// at most n CTAs.  asynchronous: 0 = register prefetch, 1 = cp.async rings in
+// shared memory, 2 = bulk asynchronous copies of whole tiles (reduce_bulk.cuh).
+// exclusive: 1 (with asynchronous) = big CTAs that take a whole SM each (see
+// kExclusiveSharedBytes), so `ctas` is then the number of SMs the collective
+// owns while it runs; the bulk variant is always launched that way.
 struct CollectiveShape {
     int ctas;
     int asynchronous;

@@ -1,5 +1,6 @@
 // Host-side launchers for the reduction kernels in reduce_kernels.cuh.
 #include "reduce_kernels.cuh"
+#include "reduce_bulk.cuh"
 
 namespace ngb {
 namespace {
@@ -66,13 +67,58 @@ cudaError_t run_reencode_async(const EncodedShards& shards, long long first_valu
     return cudaPeekAtLastError();
 }
 
+// Bulk-copy variant: whole tiles travel as cp.async.bulk transfers; always
+// launched with CTAs that own their SM.  Needs a compile-time rank count,
+// 16-byte aligned payload AND scale arenas and a 512-aligned first value.
+template <int kBlock, int kRanks, int kStages, int kWarps, int kTile>
+cudaError_t run_reencode_bulk(const EncodedShards& shards, long long first_value, long long end_value,
+                              float reduction_scale, double* squared_sum, int* finite_status,
+                              const CollectiveShape& shape, cudaStream_t stream) {
+    constexpr size_t needed = kWarps * bulk_warp_bytes<kBlock, kRanks, kStages, kTile>();
+    static_assert(needed <= kExclusiveSharedBytes, "the rings do not fit in one SM");
+    const size_t bytes = kExclusiveSharedBytes;
+    const long long tiles = (end_value - first_value + kTile - 1) / kTile;
+    const long long work = (tiles + kWarps - 1) / kWarps;
+    long long cap = shape.ctas > 0 ? shape.ctas : sm_count();
+    if (cap > sm_count()) cap = sm_count();
+    const int grid = static_cast<int>(work < cap ? work : cap);
+    cudaError_t e;
+    if (squared_sum != nullptr) {
+        auto kernel = bfp8_reduce_reencode_bulk_kernel<kBlock, kRanks, true, kStages, kWarps, kTile>;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+        if (e != cudaSuccess) return e;
+        kernel<<<grid, kWarps * 32, bytes, stream>>>(shards, first_value, end_value, reduction_scale, squared_sum,
+                                                    finite_status);
+    } else {
+        auto kernel = bfp8_reduce_reencode_bulk_kernel<kBlock, kRanks, false, kStages, kWarps, kTile>;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+        if (e != cudaSuccess) return e;
+        kernel<<<grid, kWarps * 32, bytes, stream>>>(shards, first_value, end_value, reduction_scale, nullptr,
+                                                    finite_status);
+    }
+    return cudaPeekAtLastError();
+}
+
 template <int kBlock>
 cudaError_t dispatch_reencode(const EncodedShards& shards, long long first_value, long long end_value,
                               float reduction_scale, double* squared_sum, int* finite_status,
                               bool vector_ok, const CollectiveShape& shape, cudaStream_t stream) {
+    if (vector_ok && shape.asynchronous == 2 && first_value % 512 == 0) {
+        bool scales_aligned = true;
+        for (int k = 0; k < shards.inputs; ++k) scales_aligned = scales_aligned && aligned_to(shards.scales[k], 16);
+        for (int d = 0; d < shards.outputs; ++d) scales_aligned = scales_aligned && aligned_to(shards.out_scales[d], 16);
+        if (scales_aligned) {
+            switch (shards.inputs) {
+                case 2: return run_reencode_bulk<kBlock, 2, 8, 11, 1024>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, shape, stream);
+                case 4: return run_reencode_bulk<kBlock, 4, 4, 11, 1024>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, shape, stream);
+                case 8: return run_reencode_bulk<kBlock, 8, 4, 11, 512>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, shape, stream);
+                default: break;
+            }
+        }
+    }
 #define NGB_RING(R, S, W) \
     return run_reencode_async<kBlock, R, S, W>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, shape, stream)
-    if (vector_ok && shape.asynchronous && shape.exclusive) {
+    if (vector_ok && shape.asynchronous != 0 && shape.exclusive) {
         // rings sized for an SM of their own: ~130-150 KB of loads in flight per SM
         switch (shards.inputs) {
             case 2: NGB_RING(2, 8, 16);
@@ -81,7 +127,7 @@ cudaError_t dispatch_reencode(const EncodedShards& shards, long long first_value
             default: break;
         }
     }
-    if (vector_ok && shape.asynchronous) {
+    if (vector_ok && shape.asynchronous != 0) {
         switch (shards.inputs) {
             case 2: NGB_RING(2, 8, 8);
             case 4: NGB_RING(4, 6, 8);
@@ -128,8 +174,10 @@ void dispatch_sum(int grid, cudaStream_t stream, const EncodedInputs& in, float*
 
 CollectiveShape default_collective_shape() {
     const LaunchPolicy policy = launch_policy();
-    return CollectiveShape{policy.collective_ctas, policy.collective_async != 0 ? 1 : 0,
-                           policy.collective_async == 2 ? 1 : 0};
+    // process-wide mode: 0 register prefetch, 1 cp.async rings, 2 rings in CTAs that own
+    // their SM, 3 bulk copies (always exclusive)
+    const int mode = policy.collective_async;
+    return CollectiveShape{policy.collective_ctas, mode == 3 ? 2 : (mode != 0 ? 1 : 0), mode >= 2 ? 1 : 0};
 }
 
 cudaError_t launch_bfp8_reduce_reencode(const EncodedShards& shards, long long first_value,

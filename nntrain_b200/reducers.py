@@ -99,9 +99,10 @@ class GradientGroup:
             identifier, world, rank, device, ctypes.addressof(handle)))
         self.handle = handle.value
 
-    def configure(self, collective_ctas: int = 0, asynchronous_copies: bool = True, exclusive_sms: bool = False):
+    def configure(self, collective_ctas: int = 0, asynchronous_copies: int = 1, exclusive_sms: bool = False):
         """Launch shape of THIS group's all-reduce kernels (other groups in the
-        process keep theirs)."""
+        process keep theirs).  asynchronous_copies: 0 register prefetch, 1
+        cp.async rings, 2 bulk asynchronous copies of whole tiles."""
         check("gradient_group_configure", load().nntrain_gradient_group_configure(
             self.handle, collective_ctas, int(asynchronous_copies), int(exclusive_sms)))
 
@@ -322,7 +323,7 @@ class Bfp8ArenaAllReduce:
             overlapped = world > 1 and len(self.spans) > 1
             sms = torch.cuda.get_device_properties(device).multi_processor_count
             if collective_exclusive is None:
-                collective_exclusive = False
+                collective_exclusive = collective_async == 2
             if collective_async is None:
                 # beside codec kernels the register-prefetch kernel did better
                 # than the shared cp.async ring; alone, the ring did
@@ -334,7 +335,7 @@ class Bfp8ArenaAllReduce:
             self.collective_ctas, self.collective_async = collective_ctas, collective_async
             self.collective_exclusive = bool(collective_exclusive)
             if world > 1:
-                group.configure(collective_ctas, bool(collective_async), bool(collective_exclusive))
+                group.configure(collective_ctas, int(collective_async), bool(collective_exclusive))
             self.codec_iterations_per_cta = codec_iterations_per_cta
             if codec_iterations_per_cta is not None:
                 # the encode / decode grids have no group: this one is process-wide
@@ -593,7 +594,7 @@ class LocalGradientGroup:
             self.world, (ctypes.c_int * self.world)(*self.devices), ctypes.addressof(handle)))
         self.handle = handle.value
 
-    def configure(self, collective_ctas: int = 0, asynchronous_copies: bool = True, exclusive_sms: bool = False):
+    def configure(self, collective_ctas: int = 0, asynchronous_copies: int = 1, exclusive_sms: bool = False):
         check("gradient_group_configure", load().nntrain_gradient_group_configure(
             self.handle, collective_ctas, int(asynchronous_copies), int(exclusive_sms)))
 

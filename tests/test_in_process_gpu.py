@@ -153,8 +153,8 @@ def test_two_groups_keep_their_own_launch_shape(cuda, oracle):
     gradients = [vectors.config0_gradient(oracle, r, n) for r in range(2)]
     payload, scales, _, _ = oracle.allreduce_bfp8(gradients, 32, 0.5)
     first, second = reducers.LocalGradientGroup([0, 0]), reducers.LocalGradientGroup([0, 0])
-    first.configure(collective_ctas=3, asynchronous_copies=False)
-    second.configure(collective_ctas=2, asynchronous_copies=True, exclusive_sms=True)
+    first.configure(collective_ctas=3, asynchronous_copies=0)
+    second.configure(collective_ctas=2, asynchronous_copies=1, exclusive_sms=True)
     for group in (first, second, first):
         step = reducers.InProcessBfp8AllReduce(group, n, 32, reduction_scale=0.5, write_fp32=False)
         step.enqueue([to(0, g) for g in gradients])

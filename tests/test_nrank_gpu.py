@@ -167,3 +167,35 @@ def test_non_finite_gradient_fails_complete(cuda, oracle):
         step.complete()
     step.close()
     group.close()
+
+
+@pytest.mark.parametrize("mode", (0, 1, 2, 3))
+@pytest.mark.parametrize("world", (2, 4, 8))
+@pytest.mark.parametrize("block", (32, 128))
+def test_every_way_of_fetching_the_shards_gives_the_same_bits(cuda, oracle, lib, mode, world, block):
+    """The owner kernel's four forms -- register prefetch, cp.async rings, rings
+    in CTAs that own their SM, bulk asynchronous copies -- on emulated ranks,
+    with a ragged end and a shard that starts in the middle of the arena."""
+    n = 6 * 65536 + 1024 + 333
+    gradients = [vectors.config0_gradient(oracle, r, n) for r in range(world)]
+    scale = 1.0 / world
+    expect_payload, expect_scales, _, expect_sq = oracle.allreduce_bfp8(gradients, block, scale)
+    assert lib.nntrain_gradient_configure_collective(mode) == 0
+    assert lib.nntrain_gradient_configure(2, 5) == 0          # few CTAs: every warp loops over several tiles
+    try:
+        for _ in range(2):
+            payloads, scales = encode_on_device(gradients, block)
+            sq = torch.zeros(1, dtype=torch.float64, device="cuda")
+            flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+            for rank in range(world):
+                first, end = reducers.shard_range(n, world, rank)
+                reducers.reduce_shards_bfp8(0, payloads, scales, payloads, scales, first, end, block, scale, sq, flag)
+            torch.cuda.synchronize()
+            for rank in range(world):
+                assert_bits_equal(host(payloads[rank]), expect_payload, f"payload on rank {rank}, mode {mode}")
+                assert_bits_equal(host(scales[rank]), expect_scales, f"scales on rank {rank}, mode {mode}")
+            assert int(flag.item()) == 0
+            assert sq.item() == pytest.approx(expect_sq, rel=1e-12)
+    finally:
+        assert lib.nntrain_gradient_configure_collective(1) == 0
+        assert lib.nntrain_gradient_configure(2, 0) == 0

@@ -270,6 +270,25 @@ def run_reference_arm(args, rank: int, world: int):
     emit(line)
 
 
+def qwen2_shaped_numels(total: int):
+    """A 338-tensor list with the proportions of a Qwen2-1.5B parameter list
+    (embedding, 28 x {q, k, v, o, gate, up, down, biases, norms}, final norm),
+    scaled to `total` values; every tensor at least one value, sizes odd on
+    purpose so tensors start at unaligned offsets."""
+    hidden, layers, kv, inter, vocab = 1536, 28, 256, 8960, 151936
+    numels = [vocab * hidden]
+    for _ in range(layers):
+        numels += [hidden * hidden, hidden, hidden * kv, kv, hidden * kv, kv, hidden * hidden,
+                   hidden * inter, hidden * inter, inter * hidden, hidden, hidden]
+    numels += [hidden]
+    full = sum(numels)
+    if total == full:
+        return numels
+    scaled = [max(1, n * total // full) for n in numels]
+    scaled[0] += total - sum(scaled)
+    return scaled
+
+
 # ---- every kernel alone ---------------------------------------------------------------
 def reference_kernel_cases(torch, E, arena, scratch, payload, scales, scales128, bf16):
     """The reference project's own kernels (compiled unmodified for sm_100a
@@ -297,7 +316,22 @@ def reference_kernel_cases(torch, E, arena, scratch, payload, scales, scales128,
         return call
 
     n = int(E)
-    return [
+    import numpy as np
+    numels = qwen2_shaped_numels(n)
+    bounds = np.concatenate([[0], np.cumsum(numels)]).astype(np.int64)
+    tensor_scales = torch.zeros(len(numels), dtype=torch.float32, device="cuda")
+
+    def publish_per_tensor():
+        status = 0
+        for t in range(len(numels)):
+            a, b = int(bounds[t]), int(bounds[t + 1])
+            status |= ref.nntrain_bfp8_gradient_quantize_accumulate(
+                0, ctypes.c_void_p(scratch.data_ptr() + 4 * a), ctypes.c_void_p(payload.data_ptr() + a),
+                ctypes.c_void_p(tensor_scales.data_ptr() + 4 * t), b - a, p(flag), p(sq), None)
+        return status
+
+    extra = [("publish 338 tensors, one launch train (3 stream operations)", run("publish per tensor", publish_per_tensor), 13.0 * E)]
+    return extra + [
         ("encode block32", run("quantize", lambda: ref.nntrain_cuda_bfp8_quantize_f32(0, p(arena), p(payload), p(scales), n, 32, None)), 5.125 * E),
         ("encode block128", run("quantize", lambda: ref.nntrain_cuda_bfp8_quantize_f32(0, p(arena), p(payload), p(scales128), n, 128, None)), (5 + 4 / 128) * E),
         ("encode tensor-wide (3 passes)", run("quantize", lambda: ref.nntrain_cuda_bfp8_quantize_f32(0, p(arena), p(payload), p(scale1), n, n, None)), 9.0 * E),
@@ -366,6 +400,26 @@ def time_kernels(args):
         ("squared sum bfp8", lambda: GradientNorm.squared_sum(0, GradientNorm.BFP8, payload, sq, scales, 32, flag), 1.125 * E),
         ("clip bfp8 scales", lambda: GradientNorm.clip_apply(0, GradientNorm.BFP8, scales, multiplier=0.999), 0.25 * E),
         ("clip fp32", lambda: GradientNorm.clip_apply(0, GradientNorm.FP32, scratch, multiplier=0.999), 8.0 * E),
+    ]
+    # the tensor-wide reducer over a 338-tensor bucket: one launch train for all
+    # tensors against one publication per tensor
+    import numpy as np
+    numels = qwen2_shaped_numels(E)
+    offsets_host = np.concatenate([[0], np.cumsum(numels)]).astype(np.int64)
+    offsets = torch.from_numpy(offsets_host).cuda()
+    tensor_scales = torch.zeros(len(numels), dtype=torch.float32, device="cuda")
+    maxima = torch.zeros(len(numels), dtype=torch.int32, device="cuda")
+
+    def publish_per_tensor():
+        for t in range(len(numels)):
+            a, b = int(offsets_host[t]), int(offsets_host[t + 1])
+            CudaBfp8GradientNative.quantize(0, scratch[a:b], payload[a:b], tensor_scales[t:t + 1], flag, sq)
+
+    cases += [
+        ("publish 338 tensors, one launch train (3 stream operations)",
+         lambda: CudaBfp8GradientNative.publish_tensors(0, scratch, payload, tensor_scales, offsets, maxima, flag, sq),
+         13.0 * E),
+        ("publish 338 tensors, one publication per tensor (338 x 4 stream operations)", publish_per_tensor, 13.0 * E),
     ]
     for n in (2, 4, 8):
         fn, nbytes = reduce_n(n)
@@ -451,11 +505,25 @@ def time_phases(args, step, pristine, arena, world, local_rank, barrier, runs: i
             0 if step.staging_payload is None else step.staging_payload.data_ptr(),
             0 if step.staging_scales is None else step.staging_scales.data_ptr(), None, stream.cuda_stream))
 
+    def allreduce_chunked():
+        # the step's own chunk plan, collective calls only: what the barriers,
+        # launches and kernel tails of the chunking cost without any codec kernel
+        for index, (start, stop) in enumerate(step.spans):
+            table_p = (ctypes.c_void_p * world)(*[p + start for p in step.payload_buffer.pointers])
+            table_s = (ctypes.c_void_p * world)(*[p + 4 * (start // BLOCK) for p in step.scales_buffer.pointers])
+            phase = (1 if index == 0 else 0) | (2 if index == len(step.spans) - 1 else 0)
+            check("allreduce", lib.nntrain_gradient_allreduce_bfp8(
+                step.group.handle, table_p, table_s, stop - start, BLOCK, 1.0 / world,
+                step.squared_sum.data_ptr(), step.finite_status.data_ptr(), step.mode, phase,
+                0 if step.staging_payload is None else step.staging_payload.data_ptr(),
+                0 if step.staging_scales is None else step.staging_scales.data_ptr(), None, stream.cuda_stream))
+
     def decode():
         CudaBfp8Native.block_decode(local_rank, step.payload, step.scales, arena, BLOCK)
 
     out = {}
-    todo = [("encode", encode)] + ([("allreduce", allreduce), ("decode", decode)] if world > 1 else [])
+    todo = [("encode", encode)] + ([("allreduce", allreduce), ("allreduce_chunked", allreduce_chunked),
+                                    ("decode", decode)] if world > 1 else [])
     for name, fn in todo:
         for _ in range(2):
             fn()
@@ -1033,7 +1101,8 @@ def run_interference(args, world, rank, local_rank, barrier):
     from nntrain_b200.library import check, load
     check("configure", load().nntrain_gradient_configure(2, step.collective_ctas))
     check("configure", load().nntrain_gradient_configure_collective(
-        3 if step.collective_async == 2 else (2 if step.collective_exclusive else int(bool(step.collective_async)))))
+        (3 if step.collective_exclusive else 4) if step.collective_async == 2
+        else (2 if step.collective_exclusive else int(bool(step.collective_async)))))
     first, end = reducers.shard_range(E, world, rank)
     payloads = step.payload_buffer.pointers
     scales = step.scales_buffer.pointers

@@ -75,7 +75,8 @@ int nntrain_gradient_configure(int codec_iterations_per_cta, int collective_ctas
  * kernels fetch their inputs when no group says otherwise: 1 (default) =
  * cp.async rings in shared memory, 0 = register prefetch, 2 = cp.async rings
  * in CTAs that take a whole SM each, 3 = bulk asynchronous copies of whole
- * tiles (CTAs own their SM).  Same results either way. */
+ * tiles in CTAs that own their SM, 4 = the same in small CTAs that share it.
+ * Same results either way. */
 int nntrain_gradient_configure_collective(int asynchronous_copies);
 /* ABI minor 36; no counterpart in the reference.  Most CTAs a persistent
  * encode / decode grid may use (only with codec_iterations_per_cta == 0);
@@ -322,7 +323,7 @@ int nntrain_gradient_group_destroy(void* group);
  * that two reducers in a process do not retune each other.  collective_ctas:
  * 0 = fill the machine, n > 0 = at most n CTAs.  asynchronous_copies: 0 =
  * register prefetch, 1 = cp.async rings, 2 = bulk asynchronous copies of whole
- * tiles (always exclusive).  exclusive_sms (needs asynchronous_copies): every
+ * tiles.  exclusive_sms (needs asynchronous_copies): every
  * CTA asks for a whole SM's shared memory, so
  * collective_ctas SMs belong to the all-reduce while it runs and the encode /
  * decode kernels of neighbouring chunks never share an SM with it. */

@@ -65,7 +65,7 @@ LaunchPolicy launch_policy() {
 
 void set_codec_ctas(int ctas) { g_codec_ctas.store(ctas > 0 ? ctas : 0, std::memory_order_relaxed); }
 
-void set_collective_async(int mode) { g_collective_async.store(mode < 0 ? 0 : (mode > 3 ? 3 : mode), std::memory_order_relaxed); }
+void set_collective_async(int mode) { g_collective_async.store(mode < 0 ? 0 : (mode > 4 ? 4 : mode), std::memory_order_relaxed); }
 
 void set_launch_policy(int codec_iterations_per_cta, int collective_ctas) {
     g_codec_iterations_per_cta.store(codec_iterations_per_cta, std::memory_order_relaxed);
@@ -158,10 +158,11 @@ NNTRAIN_EXPORT int nntrain_gradient_configure(int codec_iterations_per_cta, int 
 // inputs (ABI minor 36, no counterpart in the reference): 1 (default) =
 // cp.async rings in shared memory, 0 = register prefetch, 2 = cp.async rings
 // in CTAs that take a whole SM each, 3 = bulk asynchronous copies (whole
-// tiles per request; CTAs own their SM).  Same results either way; a group's
-// own shape (nntrain_gradient_group_configure) overrides it.
+// tiles per request) in CTAs that own their SM, 4 = the same in small CTAs that
+// share it.  Same results either way; a group's own shape
+// (nntrain_gradient_group_configure) overrides it.
 NNTRAIN_EXPORT int nntrain_gradient_configure_collective(int asynchronous_copies) {
-    if (asynchronous_copies < 0 || asynchronous_copies > 3) return static_cast<int>(cudaErrorInvalidValue);
+    if (asynchronous_copies < 0 || asynchronous_copies > 4) return static_cast<int>(cudaErrorInvalidValue);
     set_collective_async(asynchronous_copies);
     return static_cast<int>(cudaSuccess);
 }

@@ -318,7 +318,7 @@ NNTRAIN_EXPORT int nntrain_gradient_group_destroy(void* group) {
 // Launch shape of this group's all-reduce kernels (peer transport).
 // collective_ctas: 0 = fill the machine, n > 0 = at most n CTAs.
 // asynchronous_copies: 0 = register prefetch, 1 = cp.async rings, 2 = bulk
-// asynchronous copies of whole tiles (always exclusive).
+// asynchronous copies of whole tiles.
 // exclusive_sms: 1 (with asynchronous_copies) = every CTA takes a whole SM, so
 // collective_ctas SMs belong to the all-reduce while it runs and the codec
 // kernels of the neighbouring chunks keep the rest to themselves.
@@ -330,7 +330,7 @@ NNTRAIN_EXPORT int nntrain_gradient_group_configure(void* group, int collective_
     if (asynchronous_copies < 0 || asynchronous_copies > 2)
         return complete(kOpGradientGroup, -1, static_cast<int>(cudaErrorInvalidValue));
     header->shape = CollectiveShape{collective_ctas, asynchronous_copies,
-                                    (asynchronous_copies == 2 || (exclusive_sms != 0 && asynchronous_copies == 1)) ? 1 : 0};
+                                    (exclusive_sms != 0 && asynchronous_copies != 0) ? 1 : 0};
     return 0;
 }
 

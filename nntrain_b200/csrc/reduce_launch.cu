@@ -67,8 +67,9 @@ cudaError_t run_reencode_async(const EncodedShards& shards, long long first_valu
     return cudaPeekAtLastError();
 }
 
-// Bulk-copy variant: whole tiles travel as cp.async.bulk transfers; always
-// launched with CTAs that own their SM.  Needs a compile-time rank count,
+// Bulk-copy variant: whole tiles travel as cp.async.bulk transfers; launched
+// either with big CTAs that own their SM or with small ones that share it.
+// Needs a compile-time rank count,
 // 16-byte aligned payload AND scale arenas and a 512-aligned first value.
 template <int kBlock, int kRanks, int kStages, int kWarps, int kTile>
 cudaError_t run_reencode_bulk(const EncodedShards& shards, long long first_value, long long end_value,
@@ -76,11 +77,11 @@ cudaError_t run_reencode_bulk(const EncodedShards& shards, long long first_value
                               const CollectiveShape& shape, cudaStream_t stream) {
     constexpr size_t needed = kWarps * bulk_warp_bytes<kBlock, kRanks, kStages, kTile>();
     static_assert(needed <= kExclusiveSharedBytes, "the rings do not fit in one SM");
-    const size_t bytes = kExclusiveSharedBytes;
+    const size_t bytes = shape.exclusive ? kExclusiveSharedBytes : needed;
     const long long tiles = (end_value - first_value + kTile - 1) / kTile;
     const long long work = (tiles + kWarps - 1) / kWarps;
     long long cap = shape.ctas > 0 ? shape.ctas : sm_count();
-    if (cap > sm_count()) cap = sm_count();
+    if (shape.exclusive && cap > sm_count()) cap = sm_count();
     const int grid = static_cast<int>(work < cap ? work : cap);
     cudaError_t e;
     if (squared_sum != nullptr) {
@@ -107,6 +108,15 @@ cudaError_t dispatch_reencode(const EncodedShards& shards, long long first_value
         bool scales_aligned = true;
         for (int k = 0; k < shards.inputs; ++k) scales_aligned = scales_aligned && aligned_to(shards.scales[k], 16);
         for (int d = 0; d < shards.outputs; ++d) scales_aligned = scales_aligned && aligned_to(shards.out_scales[d], 16);
+        if (scales_aligned && !shape.exclusive) {
+            // small CTAs (4 warps, ~80 KB of rings) that share their SM with codec CTAs
+            switch (shards.inputs) {
+                case 2: return run_reencode_bulk<kBlock, 2, 8, 4, 1024>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, shape, stream);
+                case 4: return run_reencode_bulk<kBlock, 4, 4, 4, 1024>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, shape, stream);
+                case 8: return run_reencode_bulk<kBlock, 8, 4, 4, 512>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, shape, stream);
+                default: break;
+            }
+        }
         if (scales_aligned) {
             switch (shards.inputs) {
                 case 2: return run_reencode_bulk<kBlock, 2, 8, 11, 1024>(shards, first_value, end_value, reduction_scale, squared_sum, finite_status, shape, stream);
@@ -175,9 +185,10 @@ void dispatch_sum(int grid, cudaStream_t stream, const EncodedInputs& in, float*
 CollectiveShape default_collective_shape() {
     const LaunchPolicy policy = launch_policy();
     // process-wide mode: 0 register prefetch, 1 cp.async rings, 2 rings in CTAs that own
-    // their SM, 3 bulk copies (always exclusive)
+    // their SM, 3 bulk copies in CTAs that own their SM, 4 bulk copies in small CTAs
     const int mode = policy.collective_async;
-    return CollectiveShape{policy.collective_ctas, mode == 3 ? 2 : (mode != 0 ? 1 : 0), mode >= 2 ? 1 : 0};
+    return CollectiveShape{policy.collective_ctas, mode >= 3 ? 2 : (mode != 0 ? 1 : 0),
+                           (mode == 2 || mode == 3) ? 1 : 0};
 }
 
 cudaError_t launch_bfp8_reduce_reencode(const EncodedShards& shards, long long first_value,

@@ -318,20 +318,24 @@ class Bfp8ArenaAllReduce:
                                                   device=f"cuda:{device}")
             # Overlap shape: with more than one chunk in flight the all-reduce
             # kernel runs on a high-priority stream beside the encode / decode
-            # kernels of the neighbouring chunks.  The shape belongs to the
-            # group, not to the process, so another reducer keeps its own.
+            # kernels of the neighbouring chunks.  Measured on 2 and 8 B200s: a
+            # kernel whose CTAs share their SMs with codec CTAs loses 25-30 % of
+            # its speed while those run; CTAs that own their SM do not, so the
+            # overlapped step gives the collective cp.async rings on SMs of its
+            # own (56 of 148 at 2-3 ranks, 64 from 4 ranks on) and leaves the
+            # rest to the codec kernels.  The shape belongs to the group, not to
+            # the process, so another reducer keeps its own.
             overlapped = world > 1 and len(self.spans) > 1
             sms = torch.cuda.get_device_properties(device).multi_processor_count
-            if collective_exclusive is None:
-                collective_exclusive = collective_async == 2
             if collective_async is None:
-                # beside codec kernels the register-prefetch kernel did better
-                # than the shared cp.async ring; alone, the ring did
-                collective_async = 1 if (collective_exclusive or not overlapped) else 0
+                collective_async = 1
+            if collective_exclusive is None:
+                collective_exclusive = overlapped and mode == PEER and collective_async != 0
             if collective_ctas is None:
-                collective_ctas = sms if (overlapped and mode == PEER and not collective_exclusive) else 0
                 if collective_exclusive:
-                    collective_ctas = (sms * 3) // 8
+                    collective_ctas = max(1, sms * (64 if world >= 4 else 56) // 148)
+                else:
+                    collective_ctas = sms if (overlapped and mode == PEER) else 0
             self.collective_ctas, self.collective_async = collective_ctas, collective_async
             self.collective_exclusive = bool(collective_exclusive)
             if world > 1:

@@ -169,12 +169,13 @@ def test_non_finite_gradient_fails_complete(cuda, oracle):
     group.close()
 
 
-@pytest.mark.parametrize("mode", (0, 1, 2, 3))
+@pytest.mark.parametrize("mode", (0, 1, 2, 3, 4))
 @pytest.mark.parametrize("world", (2, 4, 8))
 @pytest.mark.parametrize("block", (32, 128))
 def test_every_way_of_fetching_the_shards_gives_the_same_bits(cuda, oracle, lib, mode, world, block):
-    """The owner kernel's four forms -- register prefetch, cp.async rings, rings
-    in CTAs that own their SM, bulk asynchronous copies -- on emulated ranks,
+    """The owner kernel's forms -- register prefetch, cp.async rings, rings in
+    CTAs that own their SM, bulk asynchronous copies in big and in small CTAs
+    -- on emulated ranks,
     with a ragged end and a shard that starts in the middle of the arena."""
     n = 6 * 65536 + 1024 + 333
     gradients = [vectors.config0_gradient(oracle, r, n) for r in range(world)]

@@ -29,8 +29,9 @@
 // and walks it in rows of 128 (each lane four consecutive values, one 128-bit
 // access).  The tensor under the row is tracked incrementally from the offset
 // table (one uniform, cached load per row); a row that lies inside one tensor
-// -- nearly all of them -- takes the vector path, a row that straddles a
-// boundary is done value by value.  Per-tensor maxima are folded in registers
+// -- nearly all of them -- takes the vector path (four such rows at a time, so
+// four independent 128-bit loads per lane are in flight), a row that straddles
+// a boundary is done value by value.  Per-tensor maxima are folded in registers
 // while the tensor stays the same and flushed with one atomic per change.
 #include "bfp8_kernels.cuh"
 #include "reduce_kernels.cuh"
@@ -40,6 +41,7 @@ namespace {
 
 constexpr int kChunkValues = 4096;     // per warp
 constexpr int kRowValues = 128;
+constexpr int kBatchRows = 4;          // rows whose loads are issued together when one tensor holds them all
 
 // Index t with offsets[t] <= position < offsets[t + 1] (offsets ascending,
 // offsets[0] = 0, offsets[tensors] = total).
@@ -102,7 +104,18 @@ tensors_maxima_kernel(const float* __restrict__ arena, const long long* __restri
                 m = 0.0f;
             }
             const long long at = row + lane * 4;
-            if (row + kRowValues <= total && cursor.current_end >= row + kRowValues) {
+            if (row + kBatchRows * kRowValues <= chunk_end && cursor.current_end >= row + kBatchRows * kRowValues) {
+                // kBatchRows rows inside one tensor: all their loads in flight together
+                float4 x[kBatchRows];
+                #pragma unroll
+                for (int j = 0; j < kBatchRows; ++j) x[j] = load_f4_stream(arena + at + j * kRowValues);
+                #pragma unroll
+                for (int j = 0; j < kBatchRows; ++j) {
+                    bad |= is_non_finite(x[j].x) | is_non_finite(x[j].y) | is_non_finite(x[j].z) | is_non_finite(x[j].w);
+                    m = fmaxf(m, fmaxf(fmaxf(fabsf(x[j].x), fabsf(x[j].y)), fmaxf(fabsf(x[j].z), fabsf(x[j].w))));
+                }
+                row += (kBatchRows - 1) * kRowValues;
+            } else if (row + kRowValues <= total && cursor.current_end >= row + kRowValues) {
                 const float4 x = load_f4_stream(arena + at);
                 bad |= is_non_finite(x.x) | is_non_finite(x.y) | is_non_finite(x.z) | is_non_finite(x.w);
                 m = fmaxf(m, fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
@@ -164,7 +177,30 @@ tensors_payload_kernel(float* source, signed char* __restrict__ payload, float* 
                         scales[owner] = scale;
                 }
                 const long long at = row + lane * 4;
-                if (row + kRowValues <= total && cursor.current_end >= row + kRowValues) {
+                if (row + kBatchRows * kRowValues <= chunk_end && cursor.current_end >= row + kBatchRows * kRowValues) {
+                    float4 x[kBatchRows];
+                    #pragma unroll
+                    for (int j = 0; j < kBatchRows; ++j) x[j] = load_f4_stream(source + at + j * kRowValues);
+                    #pragma unroll
+                    for (int j = 0; j < kBatchRows; ++j) {
+                        float t0, t1, t2, t3;
+                        biased_codes_of(x[j], divisor, t0, t1, t2, t3);
+                        *reinterpret_cast<unsigned*>(payload + at + j * kRowValues) = pack_codes(t0, t1, t2, t3);
+                        float4 d;
+                        d.x = __fmul_rn(code_value(t0), scale);
+                        d.y = __fmul_rn(code_value(t1), scale);
+                        d.z = __fmul_rn(code_value(t2), scale);
+                        d.w = __fmul_rn(code_value(t3), scale);
+                        store_f4(source + at + j * kRowValues, d);
+                        if (kSquares) {
+                            squares += static_cast<double>(d.x) * static_cast<double>(d.x);
+                            squares += static_cast<double>(d.y) * static_cast<double>(d.y);
+                            squares += static_cast<double>(d.z) * static_cast<double>(d.z);
+                            squares += static_cast<double>(d.w) * static_cast<double>(d.w);
+                        }
+                    }
+                    row += (kBatchRows - 1) * kRowValues;
+                } else if (row + kRowValues <= total && cursor.current_end >= row + kRowValues) {
                     const float4 x = load_f4_stream(source + at);
                     float t0, t1, t2, t3;
                     biased_codes_of(x, divisor, t0, t1, t2, t3);
@@ -233,7 +269,37 @@ tensors_sum_kernel(TensorInputs in, float* __restrict__ reduced, const long long
                 m = 0.0f;
             }
             const long long at = row + lane * 4;
-            if (row + kRowValues <= total && cursor.current_end >= row + kRowValues) {
+            if (row + kBatchRows * kRowValues <= chunk_end && cursor.current_end >= row + kBatchRows * kRowValues) {
+                float4 sum[kBatchRows];
+                for (int k = 0; k < in.inputs; ++k) {
+                    const float s = __ldg(in.scales[k] + owner);
+                    bad |= bad_scale(s);
+                    unsigned word[kBatchRows];
+                    #pragma unroll
+                    for (int j = 0; j < kBatchRows; ++j)
+                        word[j] = __ldcs(reinterpret_cast<const unsigned*>(in.payload[k] + at + j * kRowValues)) ^ 0x80808080u;
+                    #pragma unroll
+                    for (int j = 0; j < kBatchRows; ++j) {
+                        const float t0 = __fmul_rn(byte_to_float(word[j], 0), s), t1 = __fmul_rn(byte_to_float(word[j], 1), s),
+                                    t2 = __fmul_rn(byte_to_float(word[j], 2), s), t3 = __fmul_rn(byte_to_float(word[j], 3), s);
+                        if (k == 0) { sum[j].x = t0; sum[j].y = t1; sum[j].z = t2; sum[j].w = t3; }
+                        else {
+                            sum[j].x = __fadd_rn(sum[j].x, t0); sum[j].y = __fadd_rn(sum[j].y, t1);
+                            sum[j].z = __fadd_rn(sum[j].z, t2); sum[j].w = __fadd_rn(sum[j].w, t3);
+                        }
+                    }
+                }
+                #pragma unroll
+                for (int j = 0; j < kBatchRows; ++j) {
+                    float4 r = sum[j];
+                    r.x = __fmul_rn(reduction_scale, r.x); r.y = __fmul_rn(reduction_scale, r.y);
+                    r.z = __fmul_rn(reduction_scale, r.z); r.w = __fmul_rn(reduction_scale, r.w);
+                    bad |= is_non_finite(r.x) | is_non_finite(r.y) | is_non_finite(r.z) | is_non_finite(r.w);
+                    store_f4(reduced + at + j * kRowValues, r);
+                    m = fmaxf(m, fmaxf(fmaxf(fabsf(r.x), fabsf(r.y)), fmaxf(fabsf(r.z), fabsf(r.w))));
+                }
+                row += (kBatchRows - 1) * kRowValues;
+            } else if (row + kRowValues <= total && cursor.current_end >= row + kRowValues) {
                 float4 sum;
                 for (int k = 0; k < in.inputs; ++k) {
                     const unsigned biased = __ldcs(reinterpret_cast<const unsigned*>(in.payload[k] + at)) ^ 0x80808080u;
@@ -301,7 +367,18 @@ tensors_decode_kernel(const signed char* __restrict__ payload, const float* __re
                 scale = __ldg(scales + owner);
             }
             const long long at = row + lane * 4;
-            if (row + kRowValues <= total && cursor.current_end >= row + kRowValues) {
+            if (row + kBatchRows * kRowValues <= chunk_end && cursor.current_end >= row + kBatchRows * kRowValues) {
+                unsigned word[kBatchRows];
+                #pragma unroll
+                for (int j = 0; j < kBatchRows; ++j)
+                    word[j] = __ldcs(reinterpret_cast<const unsigned*>(payload + at + j * kRowValues)) ^ 0x80808080u;
+                #pragma unroll
+                for (int j = 0; j < kBatchRows; ++j)
+                    store_f4(destination + at + j * kRowValues,
+                             make_float4(__fmul_rn(byte_to_float(word[j], 0), scale), __fmul_rn(byte_to_float(word[j], 1), scale),
+                                         __fmul_rn(byte_to_float(word[j], 2), scale), __fmul_rn(byte_to_float(word[j], 3), scale)));
+                row += (kBatchRows - 1) * kRowValues;
+            } else if (row + kRowValues <= total && cursor.current_end >= row + kRowValues) {
                 const unsigned biased = __ldcs(reinterpret_cast<const unsigned*>(payload + at)) ^ 0x80808080u;
                 store_f4(destination + at,
                          make_float4(__fmul_rn(byte_to_float(biased, 0), scale), __fmul_rn(byte_to_float(biased, 1), scale),

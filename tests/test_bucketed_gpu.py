@@ -89,7 +89,7 @@ def test_small_list_with_unaligned_tensors(cuda, oracle, world):
 
 
 def test_small_transformer_list_two_ranks(cuda, oracle):
-    """BASELINE configuration 1: 41,604,096 values, nine buckets of at most
+    """Benchmark configuration 1 (a small decoder Transformer): 41,604,096 values, nine buckets of at most
     4 Mi values (the embedding alone is oversize), two replicas, clip 1.0."""
     numels = bucketed.small_transformer_numels()
     assert sum(numels) == 41_604_096

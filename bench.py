@@ -97,6 +97,11 @@ def parse_args():
     p.add_argument("--interference", action="store_true",
                    help="N > 1: time the all-reduce kernel alone and beside memory traffic on this / the other ranks")
     p.add_argument("--only", default="", help="with --kernels: run only the cases whose name contains this")
+    p.add_argument("--graph", action="store_true",
+                   help="--config 3: record each bucket's step into a CUDA graph once and time its replays "
+                        "(the default benchmark step is always timed that way unless --eager is given)")
+    p.add_argument("--eager", action="store_true",
+                   help="time the step as some forty host calls per step instead of one graph replay")
     return p.parse_args()
 
 
@@ -743,19 +748,34 @@ def run_step_bench(args, world, rank, local_rank, barrier):
         return
 
     # -- device-resident timing: every step starts from the un-quantised gradient -----------
+    graph = None
+
     def one_step(timed_pair=None):
         arena.copy_(pristine)
         torch.cuda.synchronize()
         barrier()
         if timed_pair is not None:
             timed_pair[0].record()
-        step.enqueue(arena, MAX_NORM)
+        if graph is not None:
+            graph.replay()
+        else:
+            step.enqueue(arena, MAX_NORM)
         if timed_pair is not None:
             timed_pair[1].record()
 
     for _ in range(args.warmup):
         one_step()
     result = step.complete(MAX_NORM)
+    recorded = not args.eager
+    if recorded:
+        # the step as the reference's captured mode runs it: recorded once into a
+        # CUDA graph (local kernels, the collective's barrier / kernel / fence,
+        # clip), one replay per step afterwards
+        barrier()
+        graph = step.record(arena, MAX_NORM)
+        barrier()
+        one_step()
+        step.complete(MAX_NORM)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -767,13 +787,25 @@ def run_step_bench(args, world, rank, local_rank, barrier):
     wall_begin = time.time()
     for pair in pairs:
         one_step(pair)
-        if world > 1:
+        if world > 1 and graph is None:
             torch.cuda.synchronize()
             collective_ms.append(step.collective_begin.elapsed_time(step.collective_end))
     torch.cuda.synchronize()
     barrier()
     wall_end = time.time()
     result = step.complete(MAX_NORM)
+    if world > 1 and recorded:
+        # the collective's span inside a step needs timing events, which a
+        # recording cannot carry: two eager steps after the timed region give it
+        replay, graph = graph, None
+        for _ in range(2):
+            one_step()
+            torch.cuda.synchronize()
+            collective_ms.append(step.collective_begin.elapsed_time(step.collective_end))
+        graph = replay
+        one_step()                        # leave the buffers as a replayed step leaves them (checked below)
+        torch.cuda.synchronize()
+        result = step.complete(MAX_NORM)
     elapsed_ms = sum(a.elapsed_time(b) for a, b in pairs)
     clocks = sampler.stop(wall_begin, wall_end) if rank == 0 else None
     launches = step.kernel_launches * args.steps
@@ -789,12 +821,16 @@ def run_step_bench(args, world, rank, local_rank, barrier):
     if not args.no_parity:
         parity = check_parity(step, pristine, arena, result, world, rank, BLOCK)
 
+    # a recording holds on to the collective's resources: let it go before any buffer or
+    # group is closed
+    graph = None
+
     # -- what the step is made of ----------------------------------------------------------------
     phases = None
     if not args.no_phases:
         phases = time_phases(args, step, pristine, arena, world, local_rank, barrier, max(3, min(args.steps, 5)))
         phases["step_ms"] = round(ms_per_step, 4)
-        if world > 1:
+        if world > 1 and collective_ms:
             phases["allreduce_in_step_ms"] = round(max_over_ranks(sum(collective_ms) / len(collective_ms), world), 4)
 
     # -- roofline of the dominant kernel ---------------------------------------------------------
@@ -823,7 +859,7 @@ def run_step_bench(args, world, rank, local_rank, barrier):
                     "input": "un-quantised gradient, write-back into a second buffer",
                     "note": "frac may exceed 1: the denominator is a plain copy and part of the write-back is still in L2 when the kernel ends"}
     else:
-        in_step = phases["allreduce_in_step_ms"] if phases else ms_per_step
+        in_step = phases["allreduce_in_step_ms"] if (phases and "allreduce_in_step_ms" in phases) else ms_per_step
         achieved = wire_bytes / (in_step * 1e-3) / 1e9
         roofline = {"bound": "nvlink", "kernel": "bfp8_reduce_reencode (fused reduce-scatter + accumulate + re-encode + all-gather), in the step",
                     "achieved": achieved, "peak": NVLINK_PER_DIRECTION_GBS, "peak_kind": "nominal per direction per GPU",
@@ -906,6 +942,8 @@ def run_step_bench(args, world, rank, local_rank, barrier):
                        "transport": args.mode if world > 1 else "none (single-GPU publication)",
                        **described,
                        "reduction": "mean (reduction_scale 1/N)",
+                       "launch": ("one CUDA graph replay per step (the step recorded once after the warm-up; the "
+                                  "parity block checks a replayed step)") if recorded else "eager: about forty host calls per step",
                        "l2": "inputs (6.2 GB per rank) exceed the 126 MB L2; no flush needed",
                        "input": "every timed step starts from the un-quantised gradient (pristine copy restored "
                                 "between steps, outside the per-step event pairs); ms_per_step = sum of the "
@@ -1035,6 +1073,17 @@ def run_sweep(args, world, rank, local_rank, barrier):
             arena.copy_(pristine)
             step.enqueue(arena, MAX_NORM)
         step.complete(MAX_NORM)
+        graph = None
+        if args.graph:
+            # the whole step (local kernels, the collective's barrier / kernel /
+            # fence, clip) recorded once; a replay is one launch from the host
+            torch.cuda.synchronize()
+            barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                step.enqueue(arena, MAX_NORM)
+            torch.cuda.synchronize()
+            barrier()
         total = 0.0
         for _ in range(steps):
             arena.copy_(pristine)
@@ -1042,10 +1091,16 @@ def run_sweep(args, world, rank, local_rank, barrier):
             barrier()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            step.enqueue(arena, MAX_NORM)
+            if graph is not None:
+                graph.replay()
+            else:
+                step.enqueue(arena, MAX_NORM)
             b.record()
             torch.cuda.synchronize()
             total += a.elapsed_time(b)
+        if graph is not None:
+            step.complete(MAX_NORM)
+            del graph
         ms = max_over_ranks(total / steps, world)
         wire = 2 * (world - 1) / world * (E + 4 * step.scale_count)
         hbm_bytes = (5.125 + 5.125) * E + 2 * 1.125 * E
@@ -1063,7 +1118,8 @@ def run_sweep(args, world, rank, local_rank, barrier):
               "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
               "dtype": "f32", "data": "synthetic",
               "config": {"workload": "single-bucket BFP8 block-32 all-reduce step (encode + all-reduce + decode + clip)",
-                         "input": "un-quantised bucket restored before every timed call"},
+                         "input": "un-quantised bucket restored before every timed call",
+                         "launch": "one CUDA graph replay per step" if args.graph else "eager (about twenty host calls per step)"},
               "rows": rows})
     group.close()
     return 0

@@ -47,6 +47,8 @@ enum Operation : std::uint32_t {
     kOpGradientLocalGroup = 214,
     kOpGradientLocalAllReduce = 215,
     kOpGradientPublishTensors = 216,
+    // 217: the AdamW head that reads the encoded gradient (optimizer_head.cu)
+    kOpGradientNorm = 218,
 };
 
 struct ErrorInfo {            // layout of nntrain_native_error_info (:74-82)

@@ -328,7 +328,7 @@ NNTRAIN_EXPORT int nntrain_tensor_bf16_gradient_scale(unsigned short* values, in
 // the reference, which reads the sum of squares back to the host and clips
 // with one launch per tensor) ---------------------------------------------------
 // kind: 0 = fp32, 1 = bf16, 2 = BFP8 (values = payload, scales/block required).
-NNTRAIN_EXPORT int nntrain_gradient_squared_sum(int device, int kind, const void* values, const float* scales,
+static int gradient_squared_sum_impl(int device, int kind, const void* values, const float* scales,
                                                 long long length, int block_size, double* squared_sum,
                                                 int* finite_status, cudaStream_t stream) {
     if (!values || length <= 0 || !squared_sum || kind < 0 || kind > 2 || (kind == 2 && (!scales || block_size < 0)))
@@ -345,7 +345,7 @@ NNTRAIN_EXPORT int nntrain_gradient_squared_sum(int device, int kind, const void
 // norm_and_coefficient[0] = (float)sqrt(*squared_sum), [1] = clip coefficient
 // (1 when the norm does not exceed max_norm).  Runs on the device so the
 // clip can be enqueued behind the reduction without a host read.
-NNTRAIN_EXPORT int nntrain_gradient_clip_coefficient(int device, const double* squared_sum, float max_norm,
+static int gradient_clip_coefficient_impl(int device, const double* squared_sum, float max_norm,
                                                      float* norm_and_coefficient, cudaStream_t stream) {
     if (!squared_sum || !norm_and_coefficient || !(max_norm > 0.0f))
         return static_cast<int>(cudaErrorInvalidValue);
@@ -360,7 +360,7 @@ NNTRAIN_EXPORT int nntrain_gradient_clip_coefficient(int device, const double* s
 // `coefficient` is non-null the multiplier is coefficient[1] read on the
 // device (the output of nntrain_gradient_clip_coefficient), `multiplier` is
 // ignored, and a coefficient of exactly 1 leaves the arena untouched.
-NNTRAIN_EXPORT int nntrain_gradient_clip_apply(int device, int kind, void* values, long long count,
+static int gradient_clip_apply_impl(int device, int kind, void* values, long long count,
                                                float multiplier, const float* coefficient, cudaStream_t stream) {
     if (!values || count <= 0 || kind < 0 || kind > 2) return static_cast<int>(cudaErrorInvalidValue);
     if (!coefficient && (!std::isfinite(multiplier) || !(multiplier > 0.0f)))
@@ -370,4 +370,17 @@ NNTRAIN_EXPORT int nntrain_gradient_clip_apply(int device, int kind, void* value
     if (kind == 0) return static_cast<int>(launch_f32_scale(static_cast<float*>(values), count, multiplier, stream, coefficient));
     if (kind == 1) return static_cast<int>(launch_bf16_scale(static_cast<unsigned short*>(values), count, multiplier, stream, coefficient));
     return static_cast<int>(launch_bfp8_scale_scales(static_cast<float*>(values), count, multiplier, coefficient, stream));
+}
+
+// failures of the ABI-minor-36 norm / clip exports are recorded in the error ring
+NNTRAIN_EXPORT int nntrain_gradient_squared_sum(int device, int kind, const void* values, const float* scales, long long length, int block_size, double* squared_sum, int* finite_status, cudaStream_t stream) {
+    return complete(kOpGradientNorm, device, gradient_squared_sum_impl(device, kind, values, scales, length, block_size, squared_sum, finite_status, stream));
+}
+
+NNTRAIN_EXPORT int nntrain_gradient_clip_coefficient(int device, const double* squared_sum, float max_norm, float* norm_and_coefficient, cudaStream_t stream) {
+    return complete(kOpGradientNorm, device, gradient_clip_coefficient_impl(device, squared_sum, max_norm, norm_and_coefficient, stream));
+}
+
+NNTRAIN_EXPORT int nntrain_gradient_clip_apply(int device, int kind, void* values, long long count, float multiplier, const float* coefficient, cudaStream_t stream) {
+    return complete(kOpGradientNorm, device, gradient_clip_apply_impl(device, kind, values, count, multiplier, coefficient, stream));
 }

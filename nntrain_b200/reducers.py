@@ -386,7 +386,8 @@ class Bfp8ArenaAllReduce:
         current = torch.cuda.current_stream(device)
         self.result.raw.zero_()
         ready = current.record_event()
-        for stream in (self.compute_stream, self.communication_stream, self.h2d_stream, self.d2h_stream):
+        for stream in (self.compute_stream, self.communication_stream, self.decode_stream, self.h2d_stream,
+                       self.d2h_stream):
             stream.wait_event(ready)
         launches = 0      # the library's own kernels (torch's 16-byte fill and copy are not counted)
         spans = self.spans
@@ -457,11 +458,30 @@ class Bfp8ArenaAllReduce:
                 self.result.coefficient.copy_(self.norm_and_coefficient[1:2])
             if host_scales is not None:
                 host_scales.copy_(self.scales, non_blocking=True)
-        self.communication_stream.wait_stream(self.decode_stream)
-        self.communication_stream.wait_stream(self.compute_stream)
-        self.communication_stream.wait_stream(self.d2h_stream)
+        # every stream that was forked from the caller's joins it again (which
+        # also makes the whole step recordable into a CUDA graph)
+        for stream in (self.decode_stream, self.compute_stream, self.d2h_stream, self.h2d_stream):
+            self.communication_stream.wait_stream(stream)
         current.wait_stream(self.communication_stream)
         self.kernel_launches = launches
+
+    def record(self, gradient: torch.Tensor, max_norm: float | None = None):
+        """Records one whole step for `gradient` into a CUDA graph and returns
+        it: `graph.replay()` then costs the host one launch instead of some forty
+        calls, and the device none of the gaps between them.  The arena's
+        address is part of the recording (the reference's captured mode also
+        relies on stable slot addresses, NNtrain.Core/Tensors/
+        CudaBfp8GradientPublicationScope.cs:12-521); every rank must record,
+        and later replay, in step with the others.  Run at least one eager step
+        first: kernels must be loaded and NCCL's channels set up before a
+        capture starts."""
+        device = self.group.device
+        torch.cuda.synchronize(device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            self.enqueue(gradient, max_norm)
+        torch.cuda.synchronize(device)
+        return graph
 
     def _result_final(self, index: int, gradient, host_payload, decode: bool, native_event=None) -> int:
         """Chunk `index` is final: behind `native_event` when given, else in

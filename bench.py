@@ -481,7 +481,7 @@ def max_over_ranks(value: float, world: int) -> float:
     return float(t.item())
 
 
-def time_phases(args, step, pristine, arena, world, local_rank, barrier, runs: int):
+def time_phases(step, pristine, arena, world, local_rank, barrier, runs: int):
     """Encode, all-reduce and decode of one whole-arena step, each timed alone
     (CUDA events, max over ranks): what the overlapped step is made of."""
     import ctypes
@@ -740,7 +740,7 @@ def run_step_bench(args, world, rank, local_rank, barrier):
     torch.cuda.synchronize()
 
     if args.phases:
-        phases = time_phases(args, step, pristine, arena, world, local_rank, barrier, max(3, min(args.steps, 10)))
+        phases = time_phases(step, pristine, arena, world, local_rank, barrier, max(3, min(args.steps, 10)))
         if rank == 0:
             emit({"phases": phases, "n_gpus": world, "elements_per_rank": E, "transport": args.mode, **described})
         step.close()
@@ -828,7 +828,7 @@ def run_step_bench(args, world, rank, local_rank, barrier):
     # -- what the step is made of ----------------------------------------------------------------
     phases = None
     if not args.no_phases:
-        phases = time_phases(args, step, pristine, arena, world, local_rank, barrier, max(3, min(args.steps, 5)))
+        phases = time_phases(step, pristine, arena, world, local_rank, barrier, max(3, min(args.steps, 5)))
         phases["step_ms"] = round(ms_per_step, 4)
         if world > 1 and collective_ms:
             phases["allreduce_in_step_ms"] = round(max_over_ranks(sum(collective_ms) / len(collective_ms), world), 4)

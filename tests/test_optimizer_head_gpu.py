@@ -7,7 +7,7 @@ import torch
 
 import vectors
 from gpu_helpers import assert_bits_equal, dev, host, misaligned
-from nntrain_b200.native import Bfp8GradientOptimizers, scale_count
+from nntrain_b200.native import Bfp8GradientOptimizers
 
 pytestmark = pytest.mark.gpu
 

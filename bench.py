@@ -98,10 +98,9 @@ def parse_args():
                    help="N > 1: time the all-reduce kernel alone and beside memory traffic on this / the other ranks")
     p.add_argument("--only", default="", help="with --kernels: run only the cases whose name contains this")
     p.add_argument("--graph", action="store_true",
-                   help="--config 3: record each bucket's step into a CUDA graph once and time its replays "
-                        "(the default benchmark step is always timed that way unless --eager is given)")
-    p.add_argument("--eager", action="store_true",
-                   help="time the step as some forty host calls per step instead of one graph replay")
+                   help="record the step into a CUDA graph once and time its replays: each bucket's step with "
+                        "--config 3; the whole-arena step otherwise (then nothing runs eagerly on the group "
+                        "afterwards: no phases, no end-to-end leg)")
     return p.parse_args()
 
 
@@ -682,6 +681,33 @@ def copy_floor_ms(arena, payload, scales, host_gradient, host_payload, host_scal
 
 
 _REAL_STDOUT = None
+_EXIT_WATCHDOG = None
+
+
+def arm_exit_watchdog(status: int, seconds: float = 60.0) -> None:
+    """The measurements are out; what is left is closing buffers, the group and
+    the process group.  Should one of those calls not return (a communicator
+    waiting for a peer that is already gone), leave with the status the run
+    earned instead of hanging the launcher."""
+    global _EXIT_WATCHDOG
+    if _EXIT_WATCHDOG is not None:
+        return
+
+    def leave():
+        print(f"teardown did not finish within {seconds:.0f} s; exiting without it", file=sys.stderr)
+        sys.stderr.flush()
+        os._exit(status)
+
+    _EXIT_WATCHDOG = threading.Timer(seconds, leave)
+    _EXIT_WATCHDOG.daemon = True
+    _EXIT_WATCHDOG.start()
+
+
+def disarm_exit_watchdog() -> None:
+    global _EXIT_WATCHDOG
+    if _EXIT_WATCHDOG is not None:
+        _EXIT_WATCHDOG.cancel()
+        _EXIT_WATCHDOG = None
 
 
 def protect_stdout():
@@ -766,7 +792,7 @@ def run_step_bench(args, world, rank, local_rank, barrier):
     for _ in range(args.warmup):
         one_step()
     result = step.complete(MAX_NORM)
-    recorded = not args.eager
+    recorded = args.graph
     if recorded:
         # the step as the reference's captured mode runs it: recorded once into a
         # CUDA graph (local kernels, the collective's barrier / kernel / fence,
@@ -794,18 +820,6 @@ def run_step_bench(args, world, rank, local_rank, barrier):
     barrier()
     wall_end = time.time()
     result = step.complete(MAX_NORM)
-    if world > 1 and recorded:
-        # the collective's span inside a step needs timing events, which a
-        # recording cannot carry: two eager steps after the timed region give it
-        replay, graph = graph, None
-        for _ in range(2):
-            one_step()
-            torch.cuda.synchronize()
-            collective_ms.append(step.collective_begin.elapsed_time(step.collective_end))
-        graph = replay
-        one_step()                        # leave the buffers as a replayed step leaves them (checked below)
-        torch.cuda.synchronize()
-        result = step.complete(MAX_NORM)
     elapsed_ms = sum(a.elapsed_time(b) for a, b in pairs)
     clocks = sampler.stop(wall_begin, wall_end) if rank == 0 else None
     launches = step.kernel_launches * args.steps
@@ -827,7 +841,7 @@ def run_step_bench(args, world, rank, local_rank, barrier):
 
     # -- what the step is made of ----------------------------------------------------------------
     phases = None
-    if not args.no_phases:
+    if not args.no_phases and not recorded:
         phases = time_phases(step, pristine, arena, world, local_rank, barrier, max(3, min(args.steps, 5)))
         phases["step_ms"] = round(ms_per_step, 4)
         if world > 1 and collective_ms:
@@ -872,7 +886,7 @@ def run_step_bench(args, world, rank, local_rank, barrier):
 
     # -- end to end: pinned host buffers in, encoded result out -----------------------------
     e2e = None
-    run_e2e = not args.no_e2e
+    run_e2e = not args.no_e2e and not recorded
     if run_e2e:
         # Every rank must enter the collective part or none: agree first on
         # whether the pinned host buffers could be had everywhere.
@@ -963,9 +977,11 @@ def run_step_bench(args, world, rank, local_rank, barrier):
                        "fp32_clipped": result.fp32_clipped},
         }
         emit(line)
+    status = 0 if (parity is None or parity["ok"]) else 3
+    arm_exit_watchdog(status)
     step.close()
     group.close()
-    return 0 if (parity is None or parity["ok"]) else 3
+    return status
 
 
 def run_bf16_bench(args, world, rank, local_rank, barrier):
@@ -1048,9 +1064,11 @@ def run_bf16_bench(args, world, rank, local_rank, barrier):
                             "traffic": None, "note": "N = 1: one rank's reduce (2+2 B/value) + clip (4 B/value)"}),
               "parity": {"ok": problems == 0, "windows": len(windows), "bf16": "exact" if problems == 0 else "MISMATCH"},
               "result": {"norm": result.norm, "clip_coefficient": result.coefficient}})
+    status = 0 if problems == 0 else 3
+    arm_exit_watchdog(status)
     step.close()
     group.close()
-    return 0 if problems == 0 else 3
+    return status
 
 
 def run_sweep(args, world, rank, local_rank, barrier):
@@ -1121,6 +1139,7 @@ def run_sweep(args, world, rank, local_rank, barrier):
                          "input": "un-quantised bucket restored before every timed call",
                          "launch": "one CUDA graph replay per step" if args.graph else "eager (about twenty host calls per step)"},
               "rows": rows})
+    arm_exit_watchdog(0)
     group.close()
     return 0
 
@@ -1220,6 +1239,7 @@ def run_interference(args, world, rank, local_rank, barrier):
               "collective_ctas": step.collective_ctas, "collective_async": step.collective_async,
               "collective_exclusive_sms": step.collective_exclusive,
               "note": "fused all-reduce kernel on the whole arena, per-rank CUDA-event time; side traffic started just before it"})
+    arm_exit_watchdog(0)
     step.close()
     group.close()
     return 0
@@ -1384,7 +1404,9 @@ def main():
     else:
         status = run_step_bench(args, world, rank, local_rank, barrier)
     if world > 1:
+        arm_exit_watchdog(status if status is not None else 0)
         dist.destroy_process_group()
+    disarm_exit_watchdog()
     return status
 
 

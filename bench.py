@@ -1406,6 +1406,12 @@ def main():
     if world > 1:
         arm_exit_watchdog(status if status is not None else 0)
         dist.destroy_process_group()
+        disarm_exit_watchdog()
+        # everything is torn down in order; skip the interpreter's own shutdown of
+        # the CUDA / NCCL libraries, which has nothing left to do for this job
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(status if status is not None else 0)
     disarm_exit_watchdog()
     return status
 

@@ -53,3 +53,27 @@ def test_scaled_tensor_list_keeps_count_and_total(bench):
     for total in (1 << 20, 64 << 20, bench.QWEN2_1P5B_ELEMENTS):
         numels = bench.qwen2_shaped_numels(total)
         assert len(numels) == 338 and sum(numels) == total and min(numels) >= 1
+
+
+def test_reference_arm_under_the_launcher_prints_one_line_from_rank_zero():
+    """`bench.py --impl reference` launched as N ranks: rank 0 alone times the
+    CPU restatement and prints the line, the other ranks leave with status 0."""
+    import json
+    import socket
+    import subprocess
+    import sys
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    done = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+         "--master-port", str(port), os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2",
+         "--steps", "1", "--warmup", "1", "--cpu-sample-elements", "65536"],
+        capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0, done.stderr[-2000:]
+    lines = [line for line in done.stdout.splitlines() if line.startswith("{")]
+    assert len(lines) == 1
+    line = json.loads(lines[0])
+    assert line["impl"] == "reference" and line["n_gpus"] == 2 and line["unit"] == "GB/s"
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["cpu_baseline"]["kind"] == "port"
+    assert line["gpu_launches"] == 0 and line["value"] > 0

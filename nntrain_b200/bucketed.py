@@ -208,10 +208,13 @@ class BucketedBfp8Reducer:
         world = len(self.ranks)
         self.kernel_launches += world * (1 + (1 if first else 0) + (2 if last else 0))
         for rank, s in enumerate(self.ranks):
-            CudaGradientBuckets.record_ready(s.device, s.reduced[bucket], s.communication_stream)
-            _wait(s.decode_stream, s.reduced[bucket])
-            arena, payload, scales = self.bucket_views(rank, bucket)
-            CudaBfp8Native.block_decode(s.device, payload, scales, arena, self.block, stream=s.decode_stream)
+            # the entry points select the rank's device for the calling thread;
+            # the guard puts the caller's own device back afterwards
+            with torch.cuda.device(s.device):
+                CudaGradientBuckets.record_ready(s.device, s.reduced[bucket], s.communication_stream)
+                _wait(s.decode_stream, s.reduced[bucket])
+                arena, payload, scales = self.bucket_views(rank, bucket)
+                CudaBfp8Native.block_decode(s.device, payload, scales, arena, self.block, stream=s.decode_stream)
             self.kernel_launches += 1
 
     def complete(self, max_norm: float | None = None) -> list[StepResult]:

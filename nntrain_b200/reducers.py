@@ -776,11 +776,15 @@ class InProcessBfp8AllReduce:
             launches += world * (1 + (1 if phase & 1 else 0) + (2 if phase & 2 else 0))
             if self.write_fp32:
                 for state in self.ranks:
-                    CudaGradientBuckets.record_ready(state.device, state.reduced[index], state.communication_stream)
-                    _wait(state.decode_stream, state.reduced[index])
-                    payload, scales = self._slices(state, start, stop)
-                    CudaBfp8Native.block_decode(state.device, payload, scales, state.gradient[start:stop],
-                                                self.block, stream=state.decode_stream)
+                    # (the entry points select the rank's device for this thread; the
+                    # guard puts the caller's own device back)
+                    with torch.cuda.device(state.device):
+                        CudaGradientBuckets.record_ready(state.device, state.reduced[index],
+                                                         state.communication_stream)
+                        _wait(state.decode_stream, state.reduced[index])
+                        payload, scales = self._slices(state, start, stop)
+                        CudaBfp8Native.block_decode(state.device, payload, scales, state.gradient[start:stop],
+                                                    self.block, stream=state.decode_stream)
                     launches += 1
         self._clipped = max_norm is not None
         for state in self.ranks:

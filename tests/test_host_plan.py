@@ -325,3 +325,35 @@ def test_concurrent_notifications_are_exactly_once():
     assert enqueued == list(range(plan.bucket_count - 1, -1, -1))
     plan.complete(step)
     plan.close()
+
+
+def test_bucket_layouts_of_the_benchmark_tensor_lists():
+    """BuildBuckets (NNtrain.Core/Training/CudaBFloat16GradientAllReduce.cs:1647-1678: target 4 Mi elements,
+    tensors never split, in parameter order) on the three model-shaped lists of the benchmark configurations."""
+    from nntrain_b200.bucketed import small_transformer_numels
+    from nntrain_b200.host_plan import build_buckets
+
+    def sizes(numels):
+        located, count = build_buckets(numels, 4 << 20)
+        out = [0] * count
+        for (bucket, offset), n in zip(located, numels):
+            assert offset == out[bucket]              # running-sum offsets inside the bucket, no padding
+            out[bucket] += n
+        return out
+
+    small = sizes(small_transformer_numels())
+    assert small == [16_384_000, 3_940_352, 3_416_064] + [3_152_384] * 5 + [2_101_760]
+    hidden, layers, kv, inter, vocab = 1536, 28, 256, 8960, 151936
+    qwen = [vocab * hidden]
+    for _ in range(layers):
+        qwen += [hidden * hidden, hidden, hidden * kv, kv, hidden * kv, kv, hidden * hidden,
+                 hidden * inter, hidden * inter, inter * hidden, hidden, hidden]
+    qwen += [hidden]
+    q = sizes(qwen)
+    assert sum(q) == 1_543_714_304 and len(q) == 142 and max(q) == 233_373_696 and min(q) == 4_608
+    gpt2 = [50257 * 768, 1024 * 768]
+    for _ in range(12):
+        gpt2 += [768 * 2304, 2304, 768 * 768, 768, 768, 768, 768 * 3072, 3072, 3072 * 768, 768, 768, 768]
+    gpt2 += [768, 768]
+    g = sizes(gpt2)
+    assert sum(g) == 124_439_808 and len(g) == 26 and max(g) == 38_597_376

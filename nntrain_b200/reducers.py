@@ -243,6 +243,38 @@ class _ResultBlock:
         return squared_sum, finite, norm, coefficient
 
 
+def chunk_spans(elements: int, world: int, chunk_elements: int | None = None,
+                chunk_plan: list[int] | None = None) -> tuple[list[tuple[int, int]], int]:
+    """The [start, stop) pieces a step cuts an arena of `elements` values into,
+    and the longest piece.  Every boundary is a multiple of 512 * world, so each
+    piece splits into `world` shards on 512-value boundaries (whole 32-, 64- and
+    128-value blocks, 16-byte aligned payload).  `chunk_elements`: equal pieces
+    of about that length.  `chunk_plan`: explicit lengths, the rest of the arena
+    becoming a last piece.  Neither, for an arena of 64 Mi values or more on
+    more than one rank: a short first piece (the wire starts early), long middle
+    ones (few barriers) and short last ones (little decode left at the end)."""
+    align = 512 * world
+    if chunk_elements is None or chunk_elements >= elements:
+        chunk_elements = elements
+    else:
+        chunk_elements = max(align, chunk_elements // align * align)
+    if chunk_plan is None and chunk_elements == elements and world > 1 and elements >= (64 << 20):
+        chunk_plan = [int(elements * f) for f in (0.03, 0.10, 0.26, 0.26, 0.20, 0.09)]
+    if chunk_plan:
+        plan = [max(align, int(c) // align * align) for c in chunk_plan]
+        spans, start = [], 0
+        for length in plan:
+            if start >= elements:
+                break
+            spans.append((start, min(start + length, elements)))
+            start += length
+        if start < elements:
+            spans.append((start, elements))
+    else:
+        spans = [(a, min(a + chunk_elements, elements)) for a in range(0, elements, chunk_elements)]
+    return spans, max(b - a for a, b in spans)
+
+
 class Bfp8ArenaAllReduce:
     """BFP8 all-reduce of one fp32 gradient arena across the group, with the
     fused global clip-norm.
@@ -273,29 +305,7 @@ class Bfp8ArenaAllReduce:
         self.group, self.elements, self.block, self.mode = group, elements, block_size, mode
         self.reduction_scale, self.write_fp32, self.clip_fp32 = reduction_scale, write_fp32, clip_fp32
         world = group.world
-        align = 512 * world
-        if chunk_elements is None or chunk_elements >= elements:
-            chunk_elements = elements
-        else:
-            chunk_elements = max(align, chunk_elements // align * align)
-        # `chunk_plan`: explicit chunk lengths instead of equal chunks, e.g. a
-        # short first chunk (the wire starts early), long middle chunks (few
-        # barriers) and a short last one (little decode left at the end).
-        if chunk_plan is None and chunk_elements == elements and world > 1 and elements >= (64 << 20):
-            chunk_plan = [int(elements * f) for f in (0.03, 0.10, 0.26, 0.26, 0.20, 0.09)]
-        if chunk_plan:
-            plan = [max(align, int(c) // align * align) for c in chunk_plan]
-            spans, start = [], 0
-            for length in plan:
-                if start >= elements:
-                    break
-                spans.append((start, min(start + length, elements)))
-                start += length
-            if start < elements:
-                spans.append((start, elements))
-            chunk_elements = max(b - a for a, b in spans)
-        else:
-            spans = [(a, min(a + chunk_elements, elements)) for a in range(0, elements, chunk_elements)]
+        spans, chunk_elements = chunk_spans(elements, world, chunk_elements, chunk_plan)
         self.spans = spans
         self.chunk = chunk_elements
         device = group.device

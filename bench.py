@@ -34,7 +34,8 @@ arena reducer on a GPT-2-small-sized arena, `--config 3` the bucket-size sweep,
 `--config 1` the bucketed reducer of a small Transformer's tensor list (all
 ranks in this process, no launcher), `--kernels` every kernel alone (with the
 reference project's own kernels on the same buffers where they are built),
-`--phases` / `--interference` what the overlapped step is made of.
+`--phases` / `--interference` what the overlapped step is made of, `--graph` the
+step recorded once into a CUDA graph and replayed.
 """
 from __future__ import annotations
 
